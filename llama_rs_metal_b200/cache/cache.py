@@ -8,6 +8,9 @@
     the pages that still hold positions inside the window and returns the others;
   - a state group keeps, per layer, one fixed-size tensor per slot, zeroed when the
     slot is taken. Llama has none; the storage exists for mixers that do.
+* A mixer that keeps several things (a CompositeRequest: keys and values beside a state, two
+  mixers side by side) gets one *cell* per thing; every cell joins the group of its kind and
+  the mixer's view is the tuple of its cells' views.
 * Slots and pages go back to the free lists when a sequence ends and are handed out
   again, lowest number first. Stale contents are never cleared: reads are bounded by
   each sequence's own length.
@@ -26,7 +29,7 @@ import numpy as np
 import torch
 
 from ..errors import CacheMemoryError, ContextError, InvalidError
-from ..parts.base import KeyValueRequest, StateRequest
+from ..parts.base import CompositeRequest, KeyValueRequest, StateRequest
 from .slots import FreeList
 
 PAGE_SIZE = 64
@@ -37,7 +40,7 @@ class KeyValueView:
     """What an attention layer gets: its pages and the group's page table."""
 
     k: torch.Tensor  # [pages, kv_heads, page_size, head_dim]
-    v: torch.Tensor
+    v: torch.Tensor  # [pages, kv_heads, page_size, value_dim]
     page_table: torch.Tensor  # int32 [max_slots, pages_per_sequence], -1 = no page
     page_size: int
     kv_heads: int
@@ -61,10 +64,11 @@ class KeyValueGroup:
                                        device=device)
         self.dirty = False
         shape = (pages, request.kv_heads, page_size, request.head_dim)
+        value_shape = (pages, request.kv_heads, page_size, request.value_dim or request.head_dim)
         # zeroed once: a kernel may load rows of a page that no token was ever stored in (they are
         # masked, but 0 x NaN would still be NaN)
         self.k = {e: torch.zeros(shape, dtype=dtype, device=device) for e in entries}
-        self.v = {e: torch.zeros(shape, dtype=dtype, device=device) for e in entries}
+        self.v = {e: torch.zeros(value_shape, dtype=dtype, device=device) for e in entries}
 
     def first_kept_page(self, length: int) -> int:
         """Lowest logical page a sequence of `length` tokens still needs."""
@@ -154,7 +158,7 @@ class Cache:
     """Slots, groups and their storage for one model.
 
     `requests[i]` is what cache entry i's mixer asked for (KeyValueRequest,
-    StateRequest or None). `max_tokens` is the most tokens live sequences hold at
+    StateRequest, a CompositeRequest of these, or None). `max_tokens` is the most tokens live sequences hold at
     any time, each sequence's count rounded up to whole pages; it sizes every
     key/value group's page pool. `max_sequence` bounds one sequence's length.
     """
@@ -175,11 +179,22 @@ class Cache:
         self.open_mask = np.zeros(max_slots, dtype=bool)      # slot is held by a sequence
         self.kv_groups: List[KeyValueGroup] = []
         self.state_groups: List[StateGroup] = []
-        self._where: Dict[int, Tuple[str, int]] = {}
-        by_request: Dict[object, List[int]] = {}
+        # a cell is one thing one cache entry keeps: (entry,) for a plain request, (entry, i, ...)
+        # for part i of a composite one; groups and their storage are keyed by cell
+        self._where: Dict[Tuple[int, ...], Tuple[str, int]] = {}
+        self._shape: Dict[int, object] = {}  # entry -> its cell, or the nested tuple of its cells
+        by_request: Dict[object, List[Tuple[int, ...]]] = {}
+
+        def cells_of(cell, request):
+            if isinstance(request, CompositeRequest):
+                return tuple(cells_of(cell + (i,), part) for i, part in enumerate(request.parts))
+            if request is None:
+                return None
+            by_request.setdefault(request, []).append(cell)
+            return cell
+
         for entry, request in enumerate(requests):
-            if request is not None:
-                by_request.setdefault(request, []).append(entry)
+            self._shape[entry] = cells_of((entry,), request)
         for request, entries in by_request.items():
             if isinstance(request, KeyValueRequest):
                 group = KeyValueGroup(request, entries, self.pages, max_slots, pages_per_sequence,
@@ -347,19 +362,30 @@ class Cache:
 
     # -- views ---------------------------------------------------------------------
     def view(self, entry: int):
-        kind, index = self._where.get(entry, (None, None))
+        """What the mixer of cache entry `entry` gets: a view, or (for a composite request) the
+        tuple of its parts' views."""
+        return self._view_of(self._shape.get(entry))
+
+    def _view_of(self, cell):
+        if cell is None:
+            return None
+        if len(cell) == 0 or not isinstance(cell[0], int):
+            return tuple(self._view_of(c) for c in cell)
+        kind, index = self._where.get(cell, (None, None))
         if kind == "kv":
             g = self.kv_groups[index]
-            return KeyValueView(g.k[entry], g.v[entry], g.table_device, g.page_size,
+            return KeyValueView(g.k[cell], g.v[cell], g.table_device, g.page_size,
                                 g.request.kv_heads, g.request.head_dim, g.request.window, index)
         if kind == "state":
-            return StateView(self.state_groups[index].state[entry])
+            return StateView(self.state_groups[index].state[cell])
         return None
 
-    def snapshot(self, slot: int, entry: int):
+    def snapshot(self, slot: int, entry):
         """Keys and values of one sequence and cache entry as [tokens, kv_heads, head_dim]
         (diagnostic copy, like crates/model-runtime/src/session.rs:45-83). Positions a
-        windowed group no longer keeps are NaN."""
+        windowed group no longer keeps are NaN. A state is copied as it is. `entry` is a cache
+        entry's number, or (entry, i, ...) for part i of a composite request."""
+        entry = (entry,) if isinstance(entry, int) else tuple(entry)
         kind, index = self._where[entry]
         if kind != "kv":
             return self.state_groups[index].state[entry][slot].clone()
@@ -367,7 +393,7 @@ class Cache:
         n = self.length(slot)
         shape = (n, g.request.kv_heads, g.request.head_dim)
         k = torch.full(shape, float("nan"), dtype=torch.float32)
-        v = torch.full(shape, float("nan"), dtype=torch.float32)
+        v = torch.full(shape[:2] + (g.request.value_dim or g.request.head_dim,), float("nan"), dtype=torch.float32)
         for p in range(n):
             page = int(g.table_host[slot][p // g.page_size])
             if page >= 0:

@@ -22,6 +22,8 @@
 // Rows of a tile beyond a sequence's length are zero-filled on the way into
 // shared memory, so stale cache contents (even NaN bit patterns) never reach a
 // product. Head sizes 32, 64 and 128; other sizes use the row-wise kernel.
+// With `slopes` (float32 per query head) a key n positions behind its query loses slope * n from
+// its score (a linear distance penalty); `out_scale` multiplies the result before it is rounded.
 #include "attention_mma.cuh"
 
 namespace {
@@ -31,7 +33,8 @@ template <int D>
 __global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
     const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ out,
-    const int* __restrict__ cu_seqlens, int q_heads, int kv_heads, float scale_log2, int window) {
+    const int* __restrict__ cu_seqlens, int q_heads, int kv_heads, float scale_log2, int window,
+    const float* __restrict__ slopes, float out_scale) {
   constexpr int STRIDE = D + 8, TILE = kTile * STRIDE;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2][64][STRIDE]
@@ -46,6 +49,7 @@ __global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
   const int q0 = qt * kTile;
   if (q0 >= len) return;
   const int kh = h / (q_heads / kv_heads);
+  const float slope_log2 = slopes != nullptr ? slopes[h] * 1.4426950408889634f : 0.f;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int row0 = q0 + 16 * warp;  // this warp's first query (position in the sequence)
 
@@ -91,7 +95,7 @@ __global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
         const int key = kt * kTile + 8 * nt + 2 * t + (e & 1);
         const int query = row0 + g + 8 * (e >> 1);
         const bool visible = key <= query && (window <= 0 || key > query - window);
-        s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+        s[nt][e] = visible ? s[nt][e] * scale_log2 - slope_log2 * static_cast<float>(query - key) : -INFINITY;
       }
     }
     softmax_update<D, 8>(s, o, m, l);
@@ -105,7 +109,7 @@ __global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
     total += __shfl_xor_sync(0xffffffffu, total, 2);
     const int row = row0 + g + 8 * half;
     if (row >= len) continue;
-    const float inv = 1.0f / total;
+    const float inv = out_scale / total;
     __nv_bfloat16* dst = out + (static_cast<size_t>(start + row) * q_heads + h) * D;
 #pragma unroll
     for (int dn = 0; dn < D / 8; ++dn)
@@ -125,7 +129,7 @@ __global__ __launch_bounds__(kThreads) void attention_extend_tiled_kernel(
     const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out,
     const int* __restrict__ cu_seqlens, const int* __restrict__ page_table, int table_stride,
     const int* __restrict__ slots, const int* __restrict__ kv_lens, int q_heads, int kv_heads,
-    float scale_log2, int window) {
+    float scale_log2, int window, const float* __restrict__ slopes, float out_scale) {
   constexpr int STRIDE = D + 8, TILE = kTile * STRIDE;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2][64][STRIDE]
@@ -139,6 +143,7 @@ __global__ __launch_bounds__(kThreads) void attention_extend_tiled_kernel(
   if (q0 >= n) return;
   const int len = kv_lens[b], before = len - n;
   const int kh = h / (q_heads / kv_heads);
+  const float slope_log2 = slopes != nullptr ? slopes[h] * 1.4426950408889634f : 0.f;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int row0 = q0 + 16 * warp;  // this warp's first query, counted within the portion
   const int* table = page_table + static_cast<size_t>(slots[b]) * table_stride;
@@ -190,7 +195,7 @@ __global__ __launch_bounds__(kThreads) void attention_extend_tiled_kernel(
         const int key = kt * kTile + 8 * nt + 2 * t + (e & 1);
         const int query = before + row0 + g + 8 * (e >> 1);  // position in the sequence
         const bool visible = key <= query && (window <= 0 || key > query - window);
-        s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+        s[nt][e] = visible ? s[nt][e] * scale_log2 - slope_log2 * static_cast<float>(query - key) : -INFINITY;
       }
     }
     softmax_update<D, 8>(s, o, m, l);
@@ -204,7 +209,7 @@ __global__ __launch_bounds__(kThreads) void attention_extend_tiled_kernel(
     total += __shfl_xor_sync(0xffffffffu, total, 2);
     const int row = row0 + g + 8 * half;
     if (row >= n) continue;
-    const float inv = 1.0f / total;
+    const float inv = out_scale / total;
     __nv_bfloat16* dst = out + (static_cast<size_t>(start + row) * q_heads + h) * D;
 #pragma unroll
     for (int dn = 0; dn < D / 8; ++dn)
@@ -222,7 +227,7 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
     const __nv_bfloat16* __restrict__ v_pages, float* __restrict__ partials,
     const int* __restrict__ page_table, int table_stride, const int* __restrict__ slots,
     const int* __restrict__ kv_lens, int q_heads, int kv_heads, int row_groups, float scale_log2,
-    int window, int n_splits) {
+    int window, int n_splits, const float* __restrict__ slopes) {
   // no early griddepcontrol.launch_dependents: the kernels after attention trigger at once in their
   // turn, and a whole layer's kernels scheduled behind a running attention made decode steps slower
   constexpr int STRIDE = D + 8, TILE = kTile * STRIDE;
@@ -239,6 +244,12 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 
   const int len = kv_lens[b];
+  // the distance penalty of the two query heads (rows g and g + 8 of the tile) this thread holds
+  float slope_log2[2] = {0.f, 0.f};
+  if (slopes != nullptr) {
+    if (g < rows) slope_log2[0] = slopes[head0 + g] * 1.4426950408889634f;
+    if (g + 8 < rows) slope_log2[1] = slopes[head0 + g + 8] * 1.4426950408889634f;
+  }
   const int first_key = window > 0 ? max(0, len - window) : 0;
   const int page_first = first_key / kTile, page_end = (len + kTile - 1) / kTile;
   const int n_pages = page_end - page_first;
@@ -282,7 +293,7 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
     scores<D, 2>(s, qa, Ks + stage * TILE + 16 * warp * STRIDE);
-    if ((p + 1) * kTile <= len && p * kTile >= first_key) {  // a page wholly inside the visible range
+    if (slopes == nullptr && (p + 1) * kTile <= len && p * kTile >= first_key) {  // a page wholly inside the visible range
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
@@ -294,7 +305,8 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
         for (int e = 0; e < 4; ++e) {
           const int key = p * kTile + 16 * warp + 8 * nt + 2 * t + (e & 1);
           const bool visible = key < len && key >= first_key;
-          s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+          s[nt][e] = visible ? s[nt][e] * scale_log2 - slope_log2[e >> 1] * static_cast<float>(len - 1 - key)
+                             : -INFINITY;
         }
       }
     }
@@ -348,7 +360,7 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
 // Branch-free and in chunks of 8 parts, so that a chunk's loads are all in flight together.
 template <int D>
 __global__ void attention_merge_kernel(const float* __restrict__ partials,
-                                       __nv_bfloat16* __restrict__ out, int n_parts) {
+                                       __nv_bfloat16* __restrict__ out, int n_parts, float out_scale) {
   pdl_trigger();  // a small kernel: let the next one start (and prefetch its weights) right away
   pdl_wait();
   const float* src = partials + static_cast<size_t>(blockIdx.x) * n_parts * (D + 2);
@@ -379,13 +391,15 @@ __global__ void attention_merge_kernel(const float* __restrict__ partials,
         mass = fmaf(li[u], w, mass);
       }
     }
-    out[static_cast<size_t>(blockIdx.x) * D + d] = __float2bfloat16_rn(acc / mass);
+    out[static_cast<size_t>(blockIdx.x) * D + d] =
+        __float2bfloat16_rn(out_scale == 1.0f ? acc / mass : acc / mass * out_scale);
   }
 }
 
 template <int D> int prefill_launch(const void* q, const void* k, const void* v, void* out,
                                     const int* cu_seqlens, int seqs, int max_seq_len, int q_heads,
-                                    int kv_heads, float scale, int window, cudaStream_t stream) {
+                                    int kv_heads, float scale, int window, const float* slopes,
+                                    float out_scale, cudaStream_t stream) {
   const int smem = 4 * kTile * (D + 8) * 2;
   auto kernel = attention_prefill_tiled_kernel<D>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -395,14 +409,15 @@ template <int D> int prefill_launch(const void* q, const void* k, const void* v,
   LRM_LAUNCH(kernel, grid, kThreads, smem, stream, static_cast<const __nv_bfloat16*>(q),
              static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
              static_cast<__nv_bfloat16*>(out), cu_seqlens, q_heads, kv_heads,
-             scale * 1.4426950408889634f, window);
+             scale * 1.4426950408889634f, window, slopes, out_scale);
   return 0;
 }
 
 template <int D> int extend_launch(const void* q, const void* k_pages, const void* v_pages, void* out,
                                    const int* cu_seqlens, const int* page_table, int table_stride,
                                    const int* slots, const int* kv_lens, int seqs, int max_seq_len,
-                                   int q_heads, int kv_heads, float scale, int window, cudaStream_t stream) {
+                                   int q_heads, int kv_heads, float scale, int window, const float* slopes,
+                                   float out_scale, cudaStream_t stream) {
   const int smem = 4 * kTile * (D + 8) * 2;
   auto kernel = attention_extend_tiled_kernel<D>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -412,7 +427,7 @@ template <int D> int extend_launch(const void* q, const void* k_pages, const voi
   LRM_LAUNCH(kernel, grid, kThreads, smem, stream, static_cast<const __nv_bfloat16*>(q),
              static_cast<const __nv_bfloat16*>(k_pages), static_cast<const __nv_bfloat16*>(v_pages),
              static_cast<__nv_bfloat16*>(out), cu_seqlens, page_table, table_stride, slots, kv_lens,
-             q_heads, kv_heads, scale * 1.4426950408889634f, window);
+             q_heads, kv_heads, scale * 1.4426950408889634f, window, slopes, out_scale);
   return 0;
 }
 
@@ -420,7 +435,7 @@ template <int D> int decode_launch(const void* q, const void* k_pages, const voi
                                    float* partials, void* out, const int* page_table,
                                    int table_stride, const int* slots, const int* kv_lens, int seqs,
                                    int q_heads, int kv_heads, float scale, int window, int n_splits,
-                                   cudaStream_t stream) {
+                                   const float* slopes, float out_scale, cudaStream_t stream) {
   const int smem = 4 * kTile * (D + 8) * 2;
   auto kernel = attention_decode_tiled_kernel<D>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -430,9 +445,9 @@ template <int D> int decode_launch(const void* q, const void* k_pages, const voi
   LRM_LAUNCH(kernel, grid, kThreads, smem, stream, static_cast<const __nv_bfloat16*>(q),
              static_cast<const __nv_bfloat16*>(k_pages), static_cast<const __nv_bfloat16*>(v_pages),
              partials, page_table, table_stride, slots, kv_lens, q_heads, kv_heads, row_groups,
-             scale * 1.4426950408889634f, window, n_splits);
+             scale * 1.4426950408889634f, window, n_splits, slopes);
   LRM_LAUNCH(attention_merge_kernel<D>, seqs * q_heads, D <= 64 ? 64 : 128, 0, stream, partials,
-             static_cast<__nv_bfloat16*>(out), n_splits);
+             static_cast<__nv_bfloat16*>(out), n_splits, out_scale);
   return 0;
 }
 
@@ -446,14 +461,14 @@ LRM_API int lrm_attention_tiled_supports(int head_dim, int page_size) {
 LRM_API int lrm_attention_prefill_tiled(const void* q, const void* k, const void* v, void* out,
                                         const int* cu_seqlens, int seqs, int max_seq_len,
                                         int q_heads, int kv_heads, int d, float scale, int window,
-                                        cudaStream_t stream) {
+                                        const float* slopes, float out_scale, cudaStream_t stream) {
   if (seqs <= 0 || max_seq_len <= 0) return 0;
   if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0) return LRM_BAD_ARGUMENT;
   if (q_heads > 65535 || seqs > 65535) return LRM_UNSUPPORTED;
   switch (d) {
-    case 32: return prefill_launch<32>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, stream);
-    case 64: return prefill_launch<64>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, stream);
-    case 128: return prefill_launch<128>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, stream);
+    case 32: return prefill_launch<32>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, stream);
+    case 64: return prefill_launch<64>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, stream);
+    case 128: return prefill_launch<128>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, stream);
     default: return LRM_UNSUPPORTED;
   }
 }
@@ -465,14 +480,15 @@ LRM_API int lrm_attention_extend_tiled(const void* q, const void* k_pages, const
                                        const int* cu_seqlens, const int* page_table, int table_stride,
                                        const int* slots, const int* kv_lens, int seqs, int max_seq_len,
                                        int q_heads, int kv_heads, int d, int page_size, float scale,
-                                       int window, cudaStream_t stream) {
+                                       int window, const float* slopes, float out_scale,
+                                       cudaStream_t stream) {
   if (seqs <= 0 || max_seq_len <= 0) return 0;
   if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0) return LRM_BAD_ARGUMENT;
   if (q_heads > 65535 || seqs > 65535 || page_size != kTile) return LRM_UNSUPPORTED;
   switch (d) {
-    case 32: return extend_launch<32>(q, k_pages, v_pages, out, cu_seqlens, page_table, table_stride, slots, kv_lens, seqs, max_seq_len, q_heads, kv_heads, scale, window, stream);
-    case 64: return extend_launch<64>(q, k_pages, v_pages, out, cu_seqlens, page_table, table_stride, slots, kv_lens, seqs, max_seq_len, q_heads, kv_heads, scale, window, stream);
-    case 128: return extend_launch<128>(q, k_pages, v_pages, out, cu_seqlens, page_table, table_stride, slots, kv_lens, seqs, max_seq_len, q_heads, kv_heads, scale, window, stream);
+    case 32: return extend_launch<32>(q, k_pages, v_pages, out, cu_seqlens, page_table, table_stride, slots, kv_lens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, stream);
+    case 64: return extend_launch<64>(q, k_pages, v_pages, out, cu_seqlens, page_table, table_stride, slots, kv_lens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, stream);
+    case 128: return extend_launch<128>(q, k_pages, v_pages, out, cu_seqlens, page_table, table_stride, slots, kv_lens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, stream);
     default: return LRM_UNSUPPORTED;
   }
 }
@@ -483,16 +499,17 @@ LRM_API int lrm_attention_decode_tiled(const void* q, const void* k_pages, const
                                        float* partials, void* out, const int* page_table,
                                        int table_stride, const int* slots, const int* kv_lens,
                                        int seqs, int q_heads, int kv_heads, int d, int page_size,
-                                       float scale, int window, int n_splits, cudaStream_t stream) {
+                                       float scale, int window, int n_splits, const float* slopes,
+                                       float out_scale, cudaStream_t stream) {
   if (seqs <= 0) return 0;
   if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || n_splits <= 0 ||
       partials == nullptr)
     return LRM_BAD_ARGUMENT;
   if (page_size != kTile || n_splits > 65535) return LRM_UNSUPPORTED;
   switch (d) {
-    case 32: return decode_launch<32>(q, k_pages, v_pages, partials, out, page_table, table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, window, n_splits, stream);
-    case 64: return decode_launch<64>(q, k_pages, v_pages, partials, out, page_table, table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, window, n_splits, stream);
-    case 128: return decode_launch<128>(q, k_pages, v_pages, partials, out, page_table, table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, window, n_splits, stream);
+    case 32: return decode_launch<32>(q, k_pages, v_pages, partials, out, page_table, table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, window, n_splits, slopes, out_scale, stream);
+    case 64: return decode_launch<64>(q, k_pages, v_pages, partials, out, page_table, table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, window, n_splits, slopes, out_scale, stream);
+    case 128: return decode_launch<128>(q, k_pages, v_pages, partials, out, page_table, table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, window, n_splits, slopes, out_scale, stream);
     default: return LRM_UNSUPPORTED;
   }
 }
@@ -552,7 +569,7 @@ LRM_API int lrm_attention_decode_tiled_static_scratch(const void* q, const void*
   // reads it, so nothing in the array needs clearing between calls.
   return lrm_attention_decode_tiled(q, k_pages, v_pages, partials, out, page_table, table_stride,
                                     slots, kv_lens, seqs, q_heads, kv_heads, head_dim, page_size,
-                                    scale, window, n_splits, stream);
+                                    scale, window, n_splits, nullptr, 1.0f, stream);
 }
 
 LRM_API const char* lrm_attention_static_scratch_error(int code) {

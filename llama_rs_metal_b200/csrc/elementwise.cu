@@ -90,6 +90,22 @@ LRM_API int lrm_scale_inplace(float* x, float factor, long long n, cudaStream_t 
   return 0;
 }
 
+// x[t, :] += row[:] for every row t of x [rows, width] (a vector added to the whole residual stream).
+__global__ void add_row_kernel(float* __restrict__ x, const float* __restrict__ row, int width, size_t n) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (idx < n) x[idx] += row[idx % width];
+}
+
+LRM_API int lrm_add_row(float* x, const float* row, long long rows, int width, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (x == nullptr || row == nullptr || width <= 0) return LRM_BAD_ARGUMENT;
+  const size_t n = static_cast<size_t>(rows) * width;
+  LRM_LAUNCH(add_row_kernel, blocks_for(n), 256, 0, stream, x, row, width, n);
+  return 0;
+}
+
 LRM_API int lrm_add_planes(float* x, const float* planes, int count, long long n, cudaStream_t stream) {
   if (n <= 0 || count <= 0) return 0;
   if (x == nullptr || planes == nullptr) return LRM_BAD_ARGUMENT;

@@ -1,0 +1,200 @@
+// Mixture of experts: the router's choice and the chosen experts' feed-forward.
+//
+// Router: logits z [T, E] in float32 (the product is made by the float32 matrix kernel), plus a
+// bias; the `top` largest are chosen (the lower index wins a tie) and weighted by the softmax
+// over the chosen logits only.
+//
+// Experts, token by token (lrm_moe_experts_rows): one CTA per (token, chosen expert, slice of
+// the expert's inner width). It forms its slice of
+//   y = act(W_gate x, W_up x),   clamped gate:  g = min(g, limit), u = clamp(u, -limit, limit),
+//                                               y = g sigmoid(alpha g) (u + 1)
+// and that slice's share of W_down y, scaled by the expert's weight, as one float32 plane
+// [T, width] per (choice, slice): the planes are added to the residual stream in plane order by
+// the caller (or by the next norm), so the sum has a fixed order and no atomics meet in memory.
+// A row's result depends on nothing else in the batch. This is the kernel of decoding and of
+// the float32 path; it reads an expert's matrices once per token that chose it.
+#include "common.cuh"
+
+namespace {
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                 int* __restrict__ ids, float* __restrict__ weights, int tokens, int E,
+                                 int top) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= tokens) return;
+  const float* z = logits + static_cast<size_t>(t) * E;
+  int* mine = ids + static_cast<size_t>(t) * top;
+  float* w = weights + static_cast<size_t>(t) * top;
+  float best = -INFINITY;
+  for (int c = 0; c < top; ++c) {
+    int arg = -1;
+    float val = -INFINITY;
+    for (int e = 0; e < E; ++e) {
+      const float x = z[e] + (bias != nullptr ? bias[e] : 0.f);
+      bool taken = false;
+      for (int p = 0; p < c; ++p) taken |= mine[p] == e;
+      if (!taken && (arg < 0 || x > val)) {
+        arg = e;
+        val = x;
+      }
+    }
+    mine[c] = arg;
+    w[c] = val;
+    if (c == 0) best = val;
+  }
+  float mass = 0.f;
+  for (int c = 0; c < top; ++c) {
+    w[c] = expf(w[c] - best);
+    mass += w[c];
+  }
+  for (int c = 0; c < top; ++c) w[c] /= mass;
+}
+
+template <typename T> struct Pack8;
+template <> struct Pack8<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void load(const __nv_bfloat16* p, float* f) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 v = __bfloat1622float2(h[i]);
+      f[2 * i] = v.x;
+      f[2 * i + 1] = v.y;
+    }
+  }
+};
+template <> struct Pack8<float> {
+  static constexpr int N = 4;
+  __device__ static void load(const float* p, float* f) {
+    const float4 raw = *reinterpret_cast<const float4*>(p);
+    f[0] = raw.x, f[1] = raw.y, f[2] = raw.z, f[3] = raw.w;
+  }
+};
+
+// dot of a weight row with the float32 vector `x` (shared memory), lanes of a warp across the row
+template <typename W>
+__device__ __forceinline__ float row_dot(const W* __restrict__ w, const float* __restrict__ x, int n,
+                                         bool vector_ok, int lane) {
+  float acc = 0.f;
+  constexpr int N = Pack8<W>::N;
+  if (vector_ok) {
+    for (int i = lane * N; i < n; i += 32 * N) {
+      float f[N];
+      Pack8<W>::load(w + i, f);
+#pragma unroll
+      for (int e = 0; e < N; ++e) acc = fmaf(f[e], x[i + e], acc);
+    }
+  } else {
+    for (int i = lane; i < n; i += 32) acc = fmaf(to_f32(w[i]), x[i], acc);
+  }
+  return warp_sum(acc);
+}
+
+template <typename A, typename W>
+__global__ __launch_bounds__(256) void moe_experts_rows_kernel(
+    const A* __restrict__ x, const W* __restrict__ gate, const W* __restrict__ up, const W* __restrict__ down,
+    const int* __restrict__ ids, const float* __restrict__ weights, float* __restrict__ planes, int tokens,
+    int width, int ff, int top, int slices, float limit, float alpha) {
+  extern __shared__ float smem[];
+  float* xs = smem;          // [width]
+  float* ys = smem + width;  // [slice length]
+  const int s = blockIdx.x, c = blockIdx.y, t = blockIdx.z;
+  const int per = (ff + slices - 1) / slices, f0 = s * per, f1 = min(ff, f0 + per);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  pdl_wait();
+  const int e = ids[static_cast<size_t>(t) * top + c];
+  const float weight = weights[static_cast<size_t>(t) * top + c];
+  for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f32(x[static_cast<size_t>(t) * width + i]);
+  __syncthreads();
+  const W* wg = gate + static_cast<size_t>(e) * ff * width;
+  const W* wu = up + static_cast<size_t>(e) * ff * width;
+  const W* wd = down + static_cast<size_t>(e) * width * ff;
+  const bool wide_ok = width % Pack8<W>::N == 0;
+  for (int f = f0 + warp; f < f1; f += warps) {
+    float g = row_dot(wg + static_cast<size_t>(f) * width, xs, width, wide_ok, lane);
+    float u = row_dot(wu + static_cast<size_t>(f) * width, xs, width, wide_ok, lane);
+    if (lane == 0) {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+      ys[f - f0] = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    }
+  }
+  __syncthreads();
+  // the slice's share of the down projection: a thread per output, the slice's columns in order
+  float* dst = planes + (static_cast<size_t>(c) * slices + s) * tokens * width + static_cast<size_t>(t) * width;
+  constexpr int N = Pack8<W>::N;
+  const bool slice_ok = ff % N == 0 && f0 % N == 0 && (f1 - f0) % N == 0;
+  for (int r = threadIdx.x; r < width; r += blockDim.x) {
+    const W* row = wd + static_cast<size_t>(r) * ff;
+    float acc = 0.f;
+    if (slice_ok) {
+      for (int f = f0; f < f1; f += N) {
+        float w8[N];
+        Pack8<W>::load(row + f, w8);
+#pragma unroll
+        for (int i = 0; i < N; ++i) acc = fmaf(w8[i], ys[f - f0 + i], acc);
+      }
+    } else {
+      for (int f = f0; f < f1; ++f) acc = fmaf(to_f32(row[f]), ys[f - f0], acc);
+    }
+    dst[r] = acc * weight;
+  }
+}
+
+}  // namespace
+
+LRM_API int lrm_moe_route(const float* logits, const float* bias, int* ids, float* weights, int tokens, int E,
+                          int top, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (E <= 0 || top <= 0 || top > E) return LRM_BAD_ARGUMENT;
+  LRM_LAUNCH(moe_route_kernel, (tokens + 127) / 128, 128, 0, stream, logits, bias, ids, weights, tokens, E, top);
+  return 0;
+}
+
+// How many slices of the inner width a step of `tokens` tokens is cut into: enough CTAs to fill
+// the device, no slice shorter than 64.
+LRM_API int lrm_moe_rows_slices(int tokens, int top, int ff) {
+  const long long items = static_cast<long long>(tokens) * top;
+  long long want = (2 * 148 + items - 1) / items;
+  const int most = ff / 64 > 0 ? ff / 64 : 1;
+  if (want > most) want = most;
+  return want < 1 ? 1 : static_cast<int>(want);
+}
+
+// x [T, width] (float32 or bfloat16); gate, up [E, ff, width], down [E, width, ff] (float32 or
+// bfloat16); planes float32 [top * slices, T, width].
+LRM_API int lrm_moe_experts_rows(const void* x, int x_dtype, const void* gate, const void* up, const void* down,
+                                 int w_dtype, const int* ids, const float* weights, float* planes, int tokens,
+                                 int width, int ff, int top, int slices, float limit, float alpha,
+                                 cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (width <= 0 || ff <= 0 || top <= 0 || slices <= 0 || top > 65535 || tokens > 65535) return LRM_BAD_ARGUMENT;
+  const int per = (ff + slices - 1) / slices;
+  const size_t bytes = sizeof(float) * (static_cast<size_t>(width) + per);
+  if (bytes > 200 * 1024) return LRM_UNSUPPORTED;
+  const dim3 grid(slices, top, tokens);
+#define LRM_MOE_ROWS(AT, WT)                                                                               \
+  do {                                                                                                     \
+    if (bytes > 48 * 1024) {                                                                               \
+      cudaError_t e = cudaFuncSetAttribute(moe_experts_rows_kernel<AT, WT>,                                \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);       \
+      if (e != cudaSuccess) return static_cast<int>(e);                                                    \
+    }                                                                                                      \
+    LRM_LAUNCH((moe_experts_rows_kernel<AT, WT>), grid, 256, bytes, stream, static_cast<const AT*>(x),     \
+               static_cast<const WT*>(gate), static_cast<const WT*>(up), static_cast<const WT*>(down), ids, \
+               weights, planes, tokens, width, ff, top, slices, limit, alpha);                             \
+  } while (0)
+  if (x_dtype == LRM_F32 && w_dtype == LRM_F32)
+    LRM_MOE_ROWS(float, float);
+  else if (x_dtype == LRM_BF16 && w_dtype == LRM_BF16)
+    LRM_MOE_ROWS(__nv_bfloat16, __nv_bfloat16);
+  else if (x_dtype == LRM_F32 && w_dtype == LRM_BF16)
+    LRM_MOE_ROWS(float, __nv_bfloat16);
+  else
+    return LRM_BAD_ARGUMENT;
+#undef LRM_MOE_ROWS
+  return 0;
+}

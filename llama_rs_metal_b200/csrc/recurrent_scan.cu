@@ -1,0 +1,442 @@
+// Mixers with a fixed-size state per sequence and head: a matrix S [d, dv] in float32 that every
+// token updates and reads,
+//
+//   plain decay (retention):   S <- a S + k v^T                      o = S^T q
+//   gated delta rule:          S <- diag(g) S;  u = b (v - S^T k);   S <- S + k u^T;   o = S^T q
+//
+// with a one decay per head, g one decay per head and key channel and token, b one step size per
+// head and token. Everything here is float32: the inputs are prepared in float32 by the kernels
+// below (rotation, short convolutions, unit norms, decays), the state lives in float32 in the
+// cache's state storage, one matrix per slot and head, and is carried from step to step.
+//
+// The scan: one CTA per (sequence, head, tile of value columns). Columns of S do not depend on
+// one another, so a CTA keeps its columns in registers for the whole step: thread (column j,
+// part p of P) holds rows p, p + P, p + 2P, ... of column j. Per token every thread forms, over its
+// rows, the three partial sums  r = sum g_i S_ij k_i,  s = sum g_i S_ij q_i,  c = sum k_i q_i,
+// which are added over the P parts by shuffles, and then
+//   u_j = b (v_j - r)   (or v_j without the delta rule),   o_j = s + u_j c,   S_ij <- g_i S_ij + k_i u_j,
+// which is the update above with the read-out taken after the write. Tokens are staged through
+// shared memory a chunk at a time, so the inner loop has no block-wide barrier. A step of one
+// token (decoding) and a step of a whole prompt run the same arithmetic in the same order, so
+// the state after a prompt does not depend on how it was cut.
+//
+// A sequence of padding (slot < 0) starts from zero and stores nothing.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kScanThreads = 128;
+constexpr int kChunk = 16;
+
+template <int ROWS, bool DELTA>
+__global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
+    const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+    const float* __restrict__ g, const float* __restrict__ head_decay, const float* __restrict__ beta,
+    float* __restrict__ state, float* __restrict__ out, const int* __restrict__ cu_seqlens,
+    const int* __restrict__ slots, int H, int KH, int d, int dv, int P) {
+  extern __shared__ float smem[];
+  const int DP = ROWS * P, COLS = kScanThreads / P;
+  float* qs = smem;                    // [kChunk][DP]
+  float* ks = qs + kChunk * DP;        // [kChunk][DP]
+  float* gs = ks + kChunk * DP;        // [kChunk][DP] (delta rule only)
+  float* vs = gs + (DELTA ? kChunk * DP : 0);  // [kChunk][COLS]
+  float* bs = vs + kChunk * COLS;      // [kChunk]
+
+  const int tid = threadIdx.x, pidx = tid % P, jl = tid / P;
+  const int h = blockIdx.y, b = blockIdx.z, kh = h / (H / KH);
+  const int j = blockIdx.x * COLS + jl;
+  pdl_wait();
+  const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
+  const int slot = slots[b];
+  float S[ROWS];
+  float* mine = slot >= 0 ? state + (static_cast<size_t>(slot) * H + h) * d * dv : nullptr;
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+    const int row = i * P + pidx;
+    S[i] = (mine != nullptr && row < d && j < dv) ? mine[static_cast<size_t>(row) * dv + j] : 0.f;
+  }
+  const float a = DELTA ? 1.f : head_decay[h];
+
+  for (int c0 = 0; c0 < n; c0 += kChunk) {
+    const int cn = min(kChunk, n - c0);
+    __syncthreads();
+    for (int idx = tid; idx < cn * DP; idx += kScanThreads) {
+      const int c = idx / DP, r = idx % DP;
+      const size_t tok = static_cast<size_t>(start + c0 + c);
+      const bool in = r < d;
+      qs[idx] = in ? q[(tok * KH + kh) * d + r] : 0.f;
+      ks[idx] = in ? k[(tok * KH + kh) * d + r] : 0.f;
+      if (DELTA) gs[idx] = in ? g[(tok * H + h) * d + r] : 1.f;
+    }
+    for (int idx = tid; idx < cn * COLS; idx += kScanThreads) {
+      const int c = idx / COLS, col = blockIdx.x * COLS + idx % COLS;
+      const size_t tok = static_cast<size_t>(start + c0 + c);
+      vs[idx] = col < dv ? v[(tok * H + h) * dv + col] : 0.f;
+    }
+    if (DELTA)
+      for (int c = tid; c < cn; c += kScanThreads) bs[c] = beta[static_cast<size_t>(start + c0 + c) * H + h];
+    __syncthreads();
+    for (int c = 0; c < cn; ++c) {
+      const float* qc = qs + c * DP + pidx;
+      const float* kc = ks + c * DP + pidx;
+      const float* gc = gs + c * DP + pidx;
+      float r = 0.f, s = 0.f, kq = 0.f;
+#pragma unroll
+      for (int i = 0; i < ROWS; ++i) {
+        const float ki = kc[i * P], qi = qc[i * P];
+        const float sg = S[i] * (DELTA ? gc[i * P] : a);
+        S[i] = sg;
+        if (DELTA) r = fmaf(sg, ki, r);
+        s = fmaf(sg, qi, s);
+        kq = fmaf(ki, qi, kq);
+      }
+      for (int o = 1; o < P; o <<= 1) {
+        if (DELTA) r += __shfl_xor_sync(0xffffffffu, r, o);
+        s += __shfl_xor_sync(0xffffffffu, s, o);
+        kq += __shfl_xor_sync(0xffffffffu, kq, o);
+      }
+      const float vj = vs[c * COLS + jl];
+      const float u = DELTA ? bs[c] * (vj - r) : vj;
+#pragma unroll
+      for (int i = 0; i < ROWS; ++i) S[i] = fmaf(kc[i * P], u, S[i]);
+      if (pidx == 0 && j < dv)
+        out[(static_cast<size_t>(start + c0 + c) * H + h) * dv + j] = fmaf(u, kq, s);
+    }
+  }
+  if (mine != nullptr) {
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) {
+      const int row = i * P + pidx;
+      if (row < d && j < dv) mine[static_cast<size_t>(row) * dv + j] = S[i];
+    }
+  }
+}
+
+template <int ROWS, bool DELTA>
+int launch_scan(const float* q, const float* k, const float* v, const float* g, const float* head_decay,
+                const float* beta, float* state, float* out, const int* cu_seqlens, const int* slots,
+                int seqs, int H, int KH, int d, int dv, int P, cudaStream_t stream) {
+  const int DP = ROWS * P, COLS = kScanThreads / P;
+  const size_t bytes = sizeof(float) * (static_cast<size_t>(kChunk) * DP * (DELTA ? 3 : 2) + kChunk * COLS + kChunk);
+  static bool raised = false;  // per instantiation
+  if (bytes > 48 * 1024 && !raised) {
+    cudaError_t e = cudaFuncSetAttribute(linear_scan_kernel<ROWS, DELTA>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    raised = true;
+  }
+  const dim3 grid((dv + COLS - 1) / COLS, H, seqs);
+  LRM_LAUNCH((linear_scan_kernel<ROWS, DELTA>), grid, kScanThreads, bytes, stream, q, k, v, g, head_decay, beta,
+             state, out, cu_seqlens, slots, H, KH, d, dv, P);
+  return 0;
+}
+
+// How a head's key rows are cut over threads: P parts (a power of two up to 32) of ROWS rows.
+// Few parts when the head is small (less to add up by shuffles), more when it is large (the
+// registers a thread can keep bound ROWS to 64).
+void scan_shape(int d, int* rows, int* parts) {
+  int P = 1;
+  while (P < 32 && (d + P - 1) / P > 16) P <<= 1;
+  int need = (d + P - 1) / P, R = 4;
+  while (R < need) R <<= 1;
+  *rows = R;
+  *parts = P;
+}
+
+template <bool DELTA>
+int dispatch_scan(const float* q, const float* k, const float* v, const float* g, const float* head_decay,
+                  const float* beta, float* state, float* out, const int* cu_seqlens, const int* slots,
+                  int seqs, int H, int KH, int d, int dv, cudaStream_t stream) {
+  int R, P;
+  scan_shape(d, &R, &P);
+#define LRM_SCAN_CASE(N)                                                                             \
+  case N:                                                                                            \
+    return launch_scan<N, DELTA>(q, k, v, g, head_decay, beta, state, out, cu_seqlens, slots, seqs, H, \
+                                 KH, d, dv, P, stream)
+  switch (R) {
+    LRM_SCAN_CASE(4);
+    LRM_SCAN_CASE(8);
+    LRM_SCAN_CASE(16);
+    LRM_SCAN_CASE(32);
+    LRM_SCAN_CASE(64);
+  }
+#undef LRM_SCAN_CASE
+  return LRM_UNSUPPORTED;
+}
+
+// --------------------------------------------------------------------------- read-out: norm and gate per head
+// out[t, h, :] = o / sqrt(mean(o^2) + eps) * w * act(gate[t, h, :]) * out_scale; w and gate optional.
+template <typename A, typename G>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ weight,
+                                      const G* __restrict__ gate, long long gate_stride, int gate_act,
+                                      A* __restrict__ out, int H, int dv, float eps, float out_scale) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const float* row = o + (static_cast<size_t>(t) * H + h) * dv;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < dv; j += blockDim.x) ss = fmaf(row[j], row[j], ss);
+  const float total = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(total / static_cast<float>(dv) + eps);
+  for (int j = threadIdx.x; j < dv; j += blockDim.x) {
+    float y = row[j] * inv;
+    if (weight != nullptr) y *= weight[j];
+    if (gate != nullptr) {
+      const float z = to_f32(gate[static_cast<size_t>(t) * gate_stride + h * dv + j]);
+      const float sig = 1.0f / (1.0f + expf(-z));
+      y *= gate_act == 1 ? z * sig : sig;
+    }
+    out[(static_cast<size_t>(t) * H + h) * dv + j] = from_f32<A>(y * out_scale);
+  }
+}
+
+// --------------------------------------------------------------------------- retention: rotation and key scale
+// From the fused projection row [.. q (H d) .. k (H d) .. v (H dv) ..]: q and k of every head are
+// rotated on their first `rotary` dimensions (i paired with i + rotary/2, angle = float(position) *
+// inv_freq[i], one float32 product), k is multiplied by k_scale after the rotation, v is widened.
+template <typename A>
+__global__ void retention_prepare_kernel(const A* __restrict__ proj, long long stride, int q_off, int k_off,
+                                         int v_off, const int* __restrict__ positions,
+                                         const float* __restrict__ inv_freq, int rotary, float k_scale,
+                                         float* __restrict__ qf, float* __restrict__ kf,
+                                         float* __restrict__ vf, int H, int d, int dv) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const A* row = proj + static_cast<size_t>(t) * stride;
+  const float fpos = static_cast<float>(positions[t]);
+  const int half = rotary / 2;
+  const size_t o = (static_cast<size_t>(t) * H + h) * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const A* qh = row + q_off + h * d;
+    const A* kh = row + k_off + h * d;
+    float yq = to_f32(qh[i]), yk = to_f32(kh[i]);
+    if (i < rotary) {
+      const int pair = i < half ? i : i - half;
+      const float angle = __fmul_rn(fpos, inv_freq[pair]);
+      float sn, cs;
+      sincosf(angle, &sn, &cs);
+      if (i < half) {  // first of the pair: x cos - partner sin
+        yq = fmaf(yq, cs, -__fmul_rn(to_f32(qh[i + half]), sn));
+        yk = fmaf(yk, cs, -__fmul_rn(to_f32(kh[i + half]), sn));
+      } else {         // second of the pair: x cos + partner sin
+        yq = fmaf(yq, cs, __fmul_rn(to_f32(qh[i - half]), sn));
+        yk = fmaf(yk, cs, __fmul_rn(to_f32(kh[i - half]), sn));
+      }
+    }
+    qf[o + i] = yq;
+    kf[o + i] = yk * k_scale;
+  }
+  for (int jn = threadIdx.x; jn < dv; jn += blockDim.x)
+    vf[(static_cast<size_t>(t) * H + h) * dv + jn] = to_f32(row[v_off + h * dv + jn]);
+}
+
+// --------------------------------------------------------------------------- gated delta rule: inputs
+// One CTA per (token, segment). Segments: G query heads, G key heads, H value heads (short causal
+// convolution over time per channel, then SiLU; q and k then made unit vectors per head, q also
+// times q_scale), H heads of decays g = exp(-rate_h softplus(a + dt_bias)), and one of step sizes
+// b = sigmoid(.). The convolution's channels are the columns conv_off .. conv_off + C of the
+// projection row in the order q | k | v; taps [C, n] with the last column the current token's;
+// inputs before the step's first token come from the sequence's tail [n - 1, C] in the state
+// storage (zeros at the start of a sequence).
+template <typename A>
+__device__ __forceinline__ float conv_silu(const A* __restrict__ proj, long long stride, int column, int c,
+                                           int t, int local, const float* __restrict__ taps, int n,
+                                           const float* __restrict__ tail, int C) {
+  float acc = 0.f;
+  for (int back = n - 1; back >= 0; --back) {  // oldest input first
+    const int at = local - back;
+    float x;
+    if (at >= 0)
+      x = to_f32(proj[static_cast<size_t>(t - back) * stride + column]);
+    else
+      x = tail != nullptr ? tail[static_cast<size_t>(n - 1 + at) * C + c] : 0.f;
+    acc = fmaf(taps[static_cast<size_t>(c) * n + (n - 1 - back)], x, acc);
+  }
+  return acc / (1.0f + expf(-acc));
+}
+
+template <typename A>
+__global__ void delta_prepare_kernel(const A* __restrict__ proj, long long stride, int conv_off, int b_off,
+                                     const float* __restrict__ a, long long a_stride,
+                                     const float* __restrict__ dt_bias, const float* __restrict__ rate, const float* __restrict__ taps, int n,
+                                     const float* __restrict__ tails, const int* __restrict__ cu_seqlens,
+                                     const int* __restrict__ seq_of_token, const int* __restrict__ slots,
+                                     float* __restrict__ qf, float* __restrict__ kf, float* __restrict__ vf,
+                                     float* __restrict__ gf, float* __restrict__ bf, int H, int G, int d,
+                                     int dv, float unit_eps, float q_scale) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, seg = blockIdx.y;
+  const int C = 2 * G * d + H * dv;
+  if (seg < 2 * G + H) {
+    const int b = seq_of_token[t], local = t - cu_seqlens[b], slot = slots[b];
+    const float* tail = slot >= 0 ? tails + static_cast<size_t>(slot) * (n - 1) * C : nullptr;
+    if (seg < 2 * G) {  // a query or key head: convolution, SiLU, unit vector
+      const int first = seg * d;  // q heads then k heads are contiguous channels
+      float* dst = (seg < G ? qf + (static_cast<size_t>(t) * G + seg) * d
+                            : kf + (static_cast<size_t>(t) * G + seg - G) * d);
+      float ss = 0.f;
+      // a thread keeps its channels' values between the two passes (d <= 8 * blockDim.x)
+      float mine[8];
+      int cnt = 0;
+      for (int i = threadIdx.x; i < d; i += blockDim.x, ++cnt) {
+        const float y = conv_silu(proj, stride, conv_off + first + i, first + i, t, local, taps, n, tail, C);
+        mine[cnt] = y;
+        ss = fmaf(y, y, ss);
+      }
+      const float total = block_sum(ss, scratch);
+      const float inv = (seg < G ? q_scale : 1.0f) / sqrtf(total + unit_eps);
+      cnt = 0;
+      for (int i = threadIdx.x; i < d; i += blockDim.x, ++cnt) dst[i] = mine[cnt] * inv;
+    } else {
+      const int hv = seg - 2 * G, first = 2 * G * d + hv * dv;
+      for (int i = threadIdx.x; i < dv; i += blockDim.x)
+        vf[(static_cast<size_t>(t) * H + hv) * dv + i] =
+            conv_silu(proj, stride, conv_off + first + i, first + i, t, local, taps, n, tail, C);
+    }
+  } else if (seg < 2 * G + 2 * H) {
+    const int hd = seg - 2 * G - H;
+    const float r = rate[hd];
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      const size_t at = (static_cast<size_t>(t) * H + hd) * d + i;
+      const float z = a[static_cast<size_t>(t) * a_stride + hd * d + i] + dt_bias[hd * d + i];
+      const float sp = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
+      gf[at] = expf(-r * sp);
+    }
+  } else {
+    for (int hb = threadIdx.x; hb < H; hb += blockDim.x) {
+      const float z = to_f32(proj[static_cast<size_t>(t) * stride + b_off + hb]);
+      bf[static_cast<size_t>(t) * H + hb] = 1.0f / (1.0f + expf(-z));
+    }
+  }
+}
+
+// After a step: every sequence's tail becomes the last n - 1 convolution inputs it has seen.
+// One thread per (sequence, channel), entries ascending: entry s takes input number
+// m - (n - 1) + s of the step's m tokens, or, when that is before the step, the old entry s + m,
+// which lies above every entry written so far.
+template <typename A>
+__global__ void conv_tail_update_kernel(const A* __restrict__ proj, long long stride, int conv_off, int C,
+                                        int n, float* __restrict__ tails,
+                                        const int* __restrict__ cu_seqlens, const int* __restrict__ slots) {
+  pdl_trigger();
+  pdl_wait();
+  const int b = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int slot = slots[b];
+  if (c >= C || slot < 0) return;
+  const int start = cu_seqlens[b], m = cu_seqlens[b + 1] - start;
+  float* tail = tails + static_cast<size_t>(slot) * (n - 1) * C;
+  for (int s = 0; s < n - 1; ++s) {
+    const int at = m - (n - 1) + s;
+    tail[static_cast<size_t>(s) * C + c] =
+        at >= 0 ? to_f32(proj[static_cast<size_t>(start + at) * stride + conv_off + c])
+                : tail[static_cast<size_t>(s + m) * C + c];
+  }
+}
+
+}  // namespace
+
+// q, k float32 [T, KH, d]; v float32 [T, H, dv]; out float32 [T, H, dv]; state float32
+// [slots, H, d, dv]. Without `g`: plain decay per head (head_decay [H]); with it: the gated delta
+// rule (g [T, H, d], beta [T, H]).
+LRM_API int lrm_linear_state_scan(const float* q, const float* k, const float* v, const float* g,
+                                  const float* head_decay, const float* beta, float* state, float* out,
+                                  const int* cu_seqlens, const int* slots, int seqs, int H, int KH, int d,
+                                  int dv, cudaStream_t stream) {
+  if (seqs <= 0) return 0;
+  if (H <= 0 || KH <= 0 || H % KH || d <= 0 || dv <= 0 || seqs > 65535 || H > 65535) return LRM_BAD_ARGUMENT;
+  if (d > 2048) return LRM_UNSUPPORTED;
+  if (g != nullptr) {
+    if (beta == nullptr) return LRM_BAD_ARGUMENT;
+    return dispatch_scan<true>(q, k, v, g, nullptr, beta, state, out, cu_seqlens, slots, seqs, H, KH, d, dv, stream);
+  }
+  if (head_decay == nullptr) return LRM_BAD_ARGUMENT;
+  return dispatch_scan<false>(q, k, v, nullptr, head_decay, nullptr, state, out, cu_seqlens, slots, seqs, H, KH, d,
+                              dv, stream);
+}
+
+// `gate` (type gate_dtype, may be null) is read at gate[t * gate_stride + h * dv + j].
+LRM_API int lrm_head_norm_gate(const float* o, const float* weight, const void* gate, int gate_dtype,
+                               long long gate_stride, int gate_act, void* out, int dtype, int tokens, int H,
+                               int dv, float eps, float out_scale, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (H <= 0 || H > 65535 || dv <= 0 || (gate != nullptr && gate_act != 1 && gate_act != 2)) return LRM_BAD_ARGUMENT;
+  const int threads = dv >= 256 ? 256 : ((dv + 31) / 32) * 32;
+  const dim3 grid(tokens, H);
+#define LRM_HEAD_NORM(AT, GT)                                                                              \
+  LRM_LAUNCH((head_norm_gate_kernel<AT, GT>), grid, threads, 0, stream, o, weight, static_cast<const GT*>(gate), \
+             gate_stride, gate_act, static_cast<AT*>(out), H, dv, eps, out_scale)
+  if (dtype == LRM_F32 && gate_dtype == LRM_F32)
+    LRM_HEAD_NORM(float, float);
+  else if (dtype == LRM_F32 && gate_dtype == LRM_BF16)
+    LRM_HEAD_NORM(float, __nv_bfloat16);
+  else if (dtype == LRM_BF16 && gate_dtype == LRM_F32)
+    LRM_HEAD_NORM(__nv_bfloat16, float);
+  else if (dtype == LRM_BF16 && gate_dtype == LRM_BF16)
+    LRM_HEAD_NORM(__nv_bfloat16, __nv_bfloat16);
+  else
+    return LRM_BAD_ARGUMENT;
+#undef LRM_HEAD_NORM
+  return 0;
+}
+
+LRM_API int lrm_retention_prepare(const void* proj, int dtype, long long stride, int q_off, int k_off, int v_off,
+                                  const int* positions, const float* inv_freq, int rotary, float k_scale,
+                                  float* qf, float* kf, float* vf, int tokens, int H, int d, int dv,
+                                  cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (H <= 0 || H > 65535 || d <= 0 || dv <= 0 || rotary < 0 || rotary > d || rotary % 2 ||
+      (rotary > 0 && inv_freq == nullptr))
+    return LRM_BAD_ARGUMENT;
+  const dim3 grid(tokens, H);
+  const int widest = d > dv ? d : dv;
+  const int threads = widest >= 256 ? 256 : ((widest + 31) / 32) * 32;
+  if (dtype == LRM_F32)
+    LRM_LAUNCH(retention_prepare_kernel<float>, grid, threads, 0, stream, static_cast<const float*>(proj), stride,
+               q_off, k_off, v_off, positions, inv_freq, rotary, k_scale, qf, kf, vf, H, d, dv);
+  else if (dtype == LRM_BF16)
+    LRM_LAUNCH(retention_prepare_kernel<__nv_bfloat16>, grid, threads, 0, stream,
+               static_cast<const __nv_bfloat16*>(proj), stride, q_off, k_off, v_off, positions, inv_freq, rotary,
+               k_scale, qf, kf, vf, H, d, dv);
+  else
+    return LRM_BAD_ARGUMENT;
+  return 0;
+}
+
+// `a` float32 is read at a[t * a_stride + h * d + i].
+LRM_API int lrm_delta_prepare(const void* proj, int dtype, long long stride, int conv_off, int b_off,
+                              const float* a, long long a_stride, const float* dt_bias, const float* rate, const float* taps, int n,
+                              float* tails, const int* cu_seqlens, const int* seq_of_token, const int* slots,
+                              float* qf, float* kf, float* vf, float* gf, float* bf, int tokens, int seqs, int H,
+                              int G, int d, int dv, float unit_eps, float q_scale, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || n <= 0 || seqs <= 0 || seqs > 65535) return LRM_BAD_ARGUMENT;
+  const int threads = 128;
+  if (d > 8 * threads || 2 * G + 2 * H + 1 > 65535) return LRM_UNSUPPORTED;
+  const int C = 2 * G * d + H * dv;
+  const dim3 grid(tokens, 2 * G + 2 * H + 1);
+  const dim3 tail_grid((C + 255) / 256, seqs);
+  if (dtype == LRM_F32) {
+    const float* p = static_cast<const float*>(proj);
+    LRM_LAUNCH(delta_prepare_kernel<float>, grid, threads, 0, stream, p, stride, conv_off, b_off, a, a_stride, dt_bias,
+               rate, taps, n, static_cast<const float*>(tails), cu_seqlens, seq_of_token, slots, qf, kf, vf, gf, bf, H, G,
+               d, dv, unit_eps, q_scale);
+    if (n > 1)
+      LRM_LAUNCH(conv_tail_update_kernel<float>, tail_grid, 256, 0, stream, p, stride, conv_off, C, n, tails,
+                 cu_seqlens, slots);
+  } else if (dtype == LRM_BF16) {
+    const __nv_bfloat16* p = static_cast<const __nv_bfloat16*>(proj);
+    LRM_LAUNCH(delta_prepare_kernel<__nv_bfloat16>, grid, threads, 0, stream, p, stride, conv_off, b_off, a,
+               a_stride, dt_bias, rate, taps, n, static_cast<const float*>(tails), cu_seqlens, seq_of_token, slots, qf, kf,
+               vf, gf, bf, H, G, d, dv, unit_eps, q_scale);
+    if (n > 1)
+      LRM_LAUNCH(conv_tail_update_kernel<__nv_bfloat16>, tail_grid, 256, 0, stream, p, stride, conv_off, C, n,
+                 tails, cu_seqlens, slots);
+  } else {
+    return LRM_BAD_ARGUMENT;
+  }
+  return 0;
+}

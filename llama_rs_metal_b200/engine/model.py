@@ -53,6 +53,7 @@ class DecoderModel:
         self.final_norm = build_part(NORMS, plan.final_norm, "norm")
         self._final_names = _full_names(plan.final_norm, self.final_norm)
         self.embedding: Optional[torch.Tensor] = None
+        self.stream_offsets: Optional[torch.Tensor] = None  # float32 [rows, hidden]
         self.head: Optional[LinearWeight] = None
         self.unexpected_tensors: tuple = ()  # stored names the loader skipped (set by the loader's caller)
         self._check_schedule()
@@ -63,6 +64,10 @@ class DecoderModel:
         for position, entry in enumerate(self.plan.schedule):
             if not 0 <= entry.layer < len(self.blocks):
                 raise InvalidError(f"schedule names layer {entry.layer}, the model has {len(self.blocks)}")
+            if entry.add_offset is not None:
+                rows = self.plan.stream_offsets[1] if self.plan.stream_offsets is not None else 0
+                if not 0 <= entry.add_offset < rows:
+                    raise InvalidError(f"schedule entry {position} adds offset {entry.add_offset} of {rows}")
             if entry.writes_cache:
                 if entry.cache in writers:
                     raise InvalidError(f"cache entry {entry.cache} is written by two schedule entries")
@@ -94,6 +99,8 @@ class DecoderModel:
         specs = {plan.embedding_name: TensorSpec((plan.vocab_size, plan.hidden_size))}
         if plan.head_name is not None:
             specs[plan.head_name] = TensorSpec((plan.vocab_size, plan.hidden_size))
+        if plan.stream_offsets is not None:
+            specs[plan.stream_offsets[0]] = TensorSpec((plan.stream_offsets[1], plan.hidden_size))
         for block, names in zip(self.blocks, self._names):
             for role, mapping in names.items():
                 part_specs = getattr(block, role).tensors()
@@ -109,6 +116,8 @@ class DecoderModel:
         self.embedding = tensors[self.plan.embedding_name].contiguous()
         head = self.embedding if self.plan.head_name is None else tensors[self.plan.head_name]
         self.head = LinearWeight(head)
+        if self.plan.stream_offsets is not None:  # added to the float32 stream: kept in float32
+            self.stream_offsets = tensors[self.plan.stream_offsets[0]].to(torch.float32).contiguous()
         for block, names in zip(self.blocks, self._names):
             for role, mapping in names.items():
                 getattr(block, role).bind({own: tensors[full] for own, full in mapping.items()}, rt)
@@ -162,6 +171,8 @@ class DecoderModel:
                 ctx.next_folds_pending = self.blocks[schedule[i + 1].layer].folds_pending_on_entry
             else:
                 ctx.next_folds_pending = wanted and self.final_norm.folds_pending
+            if entry.add_offset is not None:
+                hidden = ops.add_row_(hidden, self.stream_offsets[entry.add_offset])
             hidden = self.blocks[entry.layer].forward(hidden, ctx, view)
             if ctx.pending is not None and not ctx.next_folds_pending:
                 ctx.settle(hidden)  # a block left sums its successor cannot add itself

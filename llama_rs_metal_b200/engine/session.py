@@ -122,16 +122,20 @@ class Model:
             raise ContextError(self.plan.max_positions, context)
         elem = 4 if self.runtime.float32 else 2
         pages = max_batch * -(-context // PAGE_SIZE)
-        cache = 0
-        for request in self.decoder.cache_requests():
+        def need(request) -> int:
+            if request is None:
+                return 0
+            if hasattr(request, "parts"):  # several things kept by one mixer
+                return sum(need(part) for part in request.parts)
             if hasattr(request, "kv_heads"):
-                cache += 2 * pages * PAGE_SIZE * request.kv_heads * request.head_dim * elem
-            elif request is not None:
-                n = 1
-                for s in request.shape:
-                    n *= s
-                cache += max_batch * n * torch.empty((), dtype=request.dtype).element_size()
-        return MemoryEstimate(self.weight_bytes, cache)
+                width = request.head_dim + (request.value_dim or request.head_dim)
+                return pages * PAGE_SIZE * request.kv_heads * width * elem
+            n = 1
+            for s in request.shape:
+                n *= s
+            return max_batch * n * torch.empty((), dtype=request.dtype).element_size()
+
+        return MemoryEstimate(self.weight_bytes, sum(need(r) for r in self.decoder.cache_requests()))
 
     def session(self, context: int = 0, max_batch: int = 1, max_tokens: Optional[int] = None) -> "Session":
         """`context` 0 selects min(8192, the model's limit) (crates/llama-rs/src/model.rs:19-23)."""

@@ -37,12 +37,20 @@ def _tiled(q, page_size: int) -> bool:
             and bool(library.load().lrm_attention_tiled_supports(q.shape[2], page_size)))
 
 
-def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: float, window: int) -> None:
+def _plain(q, dv: int, slopes, out_scale: float) -> bool:
+    """True for attention as the tensor-core kernels compute it: values as wide as keys, no
+    distance penalty, the result not scaled."""
+    return dv == q.shape[2] and slopes is None and out_scale == 1.0
+
+
+def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: float, window: int,
+            slopes=None, out_scale: float = 1.0) -> None:
     T, Hq, d = q.shape
+    dv = v.shape[2]
     lib = library.load()
     aligned = all(t.data_ptr() % 16 == 0 for t in (q, k, v, out))
     if (not force_rowwise and not force_warp_level and q.dtype == torch.bfloat16 and aligned
-            and lib.lrm_attention_prefill_umma_supports(d)):
+            and _plain(q, dv, slopes, out_scale) and lib.lrm_attention_prefill_umma_supports(d)):
         from . import gemm_dispatch
         gemm_dispatch.mark_status_dirty()
         # Two tcgen05 kernels. The one that keeps probabilities and output in tensor memory wins on
@@ -72,15 +80,17 @@ def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: flo
                                              _ptr(gemm_dispatch._status_word(q.device)), _stream()),
               "attention_prefill_umma")
         return
-    if _tiled(q, 64):
+    if dv == d and _tiled(q, 64):
         _done(lib.lrm_attention_prefill_tiled(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(cu_seqlens),
                                               cu_seqlens.numel() - 1, max_seq_len, Hq, k.shape[1], d,
-                                              ctypes.c_float(scale), window, _stream()),
+                                              ctypes.c_float(scale), window, _ptr(slopes),
+                                              ctypes.c_float(out_scale), _stream()),
               "attention_prefill_tiled")
         return
     _done(lib.lrm_attention_packed_rowwise(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _code(q.dtype),
-                                           _ptr(cu_seqlens), _ptr(seq_of_token), T, Hq, k.shape[1], d,
-                                           ctypes.c_float(scale), window, _stream()),
+                                           _ptr(cu_seqlens), _ptr(seq_of_token), T, Hq, k.shape[1], d, dv,
+                                           ctypes.c_float(scale), window, _ptr(slopes),
+                                           ctypes.c_float(out_scale), _stream()),
           "attention_packed_rowwise")
 
 
@@ -95,44 +105,51 @@ def decode_splits(seqs: int, kv_heads: int, group: int, max_kv_len: int, window:
     return max(1, min(pages, -(-CTAS_PER_SM * SM_COUNT // ctas)))
 
 
-def decode(q, kv, out, slots, kv_lens, max_kv_len: int, scale: float, window: int) -> None:
+def decode(q, kv, out, slots, kv_lens, max_kv_len: int, scale: float, window: int,
+           slopes=None, out_scale: float = 1.0) -> None:
     B, Hq, d = q.shape
+    dv = kv.v.shape[3]
     lib = library.load()
-    if _tiled(q, kv.page_size):
+    if dv == d and _tiled(q, kv.page_size):
         splits = decode_splits(B, kv.kv_heads, Hq // kv.kv_heads, max_kv_len, window)
         partials = torch.empty((B, Hq, splits, d + 2), dtype=torch.float32, device=q.device)
         _done(lib.lrm_attention_decode_tiled(_ptr(q), _ptr(kv.k), _ptr(kv.v), _ptr(partials), _ptr(out),
                                              _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
                                              _ptr(kv_lens), B, Hq, kv.kv_heads, d, kv.page_size,
-                                             ctypes.c_float(scale), window, splits, _stream()),
+                                             ctypes.c_float(scale), window, splits, _ptr(slopes),
+                                             ctypes.c_float(out_scale), _stream()),
               "attention_decode_tiled", launches=2)
         return
     _done(lib.lrm_attention_paged_rowwise(_ptr(q), _ptr(kv.k), _ptr(kv.v), _ptr(out), _code(q.dtype),
                                           _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
-                                          _ptr(kv_lens), None, None, B, Hq, kv.kv_heads, d, kv.page_size,
-                                          ctypes.c_float(scale), window, _stream()),
+                                          _ptr(kv_lens), None, None, B, Hq, kv.kv_heads, d, dv, kv.page_size,
+                                          ctypes.c_float(scale), window, _ptr(slopes),
+                                          ctypes.c_float(out_scale), _stream()),
           "attention_paged_rowwise")
 
 
 def extend(q, kv, out, cu_seqlens, seq_of_token, positions, slots, kv_lens, max_seq_len: int, scale: float,
-           window: int) -> None:
+           window: int, slopes=None, out_scale: float = 1.0) -> None:
     """Packed queries, several per sequence, over the cache that already holds the step's keys."""
     T, Hq, d = q.shape
+    dv = kv.v.shape[3]
     lib = library.load()
-    if _tiled(q, kv.page_size):
+    if dv == d and _tiled(q, kv.page_size):
         _done(lib.lrm_attention_extend_tiled(_ptr(q), _ptr(kv.k), _ptr(kv.v), _ptr(out), _ptr(cu_seqlens),
                                              _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
                                              _ptr(kv_lens), cu_seqlens.numel() - 1, max_seq_len, Hq,
                                              kv.kv_heads, d, kv.page_size, ctypes.c_float(scale), window,
-                                             _stream()), "attention_extend_tiled")
+                                             _ptr(slopes), ctypes.c_float(out_scale), _stream()),
+              "attention_extend_tiled")
         return
     # the same arithmetic, key by key in ascending order, as the packed row-wise kernel: in
     # float32 a prompt cut into portions gives the bits of the whole prompt
     _done(lib.lrm_attention_paged_rowwise(_ptr(q), _ptr(kv.k), _ptr(kv.v), _ptr(out), _code(q.dtype),
                                           _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
                                           _ptr(kv_lens), _ptr(seq_of_token), _ptr(positions), T, Hq,
-                                          kv.kv_heads, d, kv.page_size, ctypes.c_float(scale), window,
-                                          _stream()), "attention_paged_rowwise")
+                                          kv.kv_heads, d, dv, kv.page_size, ctypes.c_float(scale), window,
+                                          _ptr(slopes), ctypes.c_float(out_scale), _stream()),
+          "attention_paged_rowwise")
 
 
 _cluster_room = {}
@@ -222,7 +239,8 @@ def decode_fused(qkv, positions, inv_freq, rotary: int, kv, dest_rows, out, slot
 
 # --------------------------------------------------------------------------- one call for a mixer
 def attend(projected, *, q_heads: int, kv_heads: int, head_dim: int, rotary, ctx, cache, writes_cache: bool,
-           cache_entry: int, scale: float, window, projection=None):
+           cache_entry: int, scale: float, window, projection=None, value_dim=None, bias=None, slopes=None,
+           out_scale: float = 1.0):
     """A layer's attention for one step: position rotation, cache write and attention, with the
     kernels chosen here for the step's phase, dtype and geometry. -> mixed heads [T, q_heads * d].
 
@@ -234,10 +252,38 @@ def attend(projected, *, q_heads: int, kv_heads: int, head_dim: int, rotary, ctx
     ctx: the StepContext; cache: the KeyValueView of `cache_entry`; window: keys a query sees, or None.
     projection: (x, weight) instead of `projected` (then None) when nothing stands between the
         projection and the rotation: a prompt's product then rotates and stores in its epilogue.
+    value_dim: head width of values when it is not head_dim; bias: float32 [projected width], added
+        to the projection; slopes: float32 [q_heads], the linear distance penalty; out_scale: factor
+        on the result. With any of these the split kernel without rotation (csrc/qkv_store.cu) takes
+        the place of the rotation kernel, and attention runs on the kernels that know them.
     """
     from . import ops
     inv_freq, width = rotary if rotary is not None else (None, 0)
     phase = ctx.phase
+    dv = head_dim if value_dim is None else value_dim
+    if bias is not None or dv != head_dim or slopes is not None or out_scale != 1.0:
+        if inv_freq is not None:
+            from ..errors import UnsupportedError
+            raise UnsupportedError("attention with a bias, a distance penalty or values of another width "
+                                   "is built without rotation")
+        if projection is not None:
+            projected = ops.linear(*projection)
+        prefill_phase = phase == "prefill"
+        q, k, v = ops.qkv_bias_store(projected, bias, q_heads, kv_heads if writes_cache else 0, head_dim, dv,
+                                     kv=cache if writes_cache else None,
+                                     dest_rows=ctx.dest_rows[cache.group] if writes_cache and cache is not None else None,
+                                     keep_packed=prefill_phase and writes_cache)
+        if prefill_phase:
+            if writes_cache:
+                ctx.fresh_kv[cache_entry] = (k, v)
+            k, v = ctx.fresh_kv[cache_entry]
+            return ops.attention_prefill(q, k, v, ctx.cu_seqlens, ctx.seq_of_token, ctx.max_seq_len, scale, window,
+                                         slopes, out_scale)
+        if phase == "decode":
+            return ops.attention_decode(q, cache, ctx.slots, ctx.kv_lens, ctx.max_kv_len, scale, window, slopes,
+                                        out_scale)
+        return ops.attention_extend(q, cache, ctx.cu_seqlens, ctx.seq_of_token, ctx.positions, ctx.slots,
+                                    ctx.kv_lens, ctx.max_seq_len, scale, window, slopes, out_scale)
     if projection is not None:
         x, weight = projection
         if (phase == "prefill" and writes_cache and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16

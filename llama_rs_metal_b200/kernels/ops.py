@@ -324,11 +324,248 @@ def linear_rope_store(x: torch.Tensor, weight: torch.Tensor, q_heads: int, kv_he
     return q, k, v
 
 
+def qkv_bias_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_heads: int, kv_heads: int, head_dim: int,
+                   value_dim: int, kv=None, dest_rows: Optional[torch.Tensor] = None, keep_packed: bool = True):
+    """Split a fused [T, Hq*d + Hk*d + Hk*dv] projection without rotation: add `bias` (float32, the
+    row's width, or None), and return (q [T,Hq,d], k [T,Hk,d] or None, v [T,Hk,dv] or None); k and
+    v are returned when `keep_packed`, and written to the paged cache view `kv` at `dest_rows`
+    when given (see rope_store)."""
+    _check(qkv, "qkv", dims=2)
+    T = qkv.shape[0]
+    width = q_heads * head_dim + kv_heads * (head_dim + value_dim)
+    if qkv.shape[1] != width:
+        raise InvalidError("qkv_bias_store: qkv width does not match the head geometry")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+        if bias.numel() != width:
+            raise InvalidError("qkv_bias_store: one bias per projected column")
+    dev = qkv.device
+    q = torch.empty((T, q_heads, head_dim), dtype=qkv.dtype, device=dev)
+    k = torch.empty((T, kv_heads, head_dim), dtype=qkv.dtype, device=dev) if keep_packed else None
+    v = torch.empty((T, kv_heads, value_dim), dtype=qkv.dtype, device=dev) if keep_packed else None
+    k_pages = v_pages = None
+    page_size = 1
+    if kv is not None and kv_heads > 0:
+        k_pages, v_pages, page_size = kv.k, kv.v, kv.page_size
+        _check(k_pages, "k pages", qkv.dtype, 4)
+        _check(v_pages, "v pages", qkv.dtype, 4)
+        _check(dest_rows, "dest_rows", torch.int32, 1)
+        if dest_rows.numel() != T:
+            raise InvalidError("qkv_bias_store: one destination row per token")
+        if (tuple(k_pages.shape[1:]) != (kv_heads, page_size, head_dim)
+                or tuple(v_pages.shape[1:]) != (kv_heads, page_size, value_dim)):
+            raise InvalidError("qkv_bias_store: cache pages do not match the head geometry")
+    _done(_lib().lrm_qkv_bias_store(_ptr(qkv), _code(qkv.dtype), _ptr(bias), _ptr(q), _ptr(k), _ptr(v),
+                                    _ptr(k_pages), _ptr(v_pages), _ptr(dest_rows if k_pages is not None else None),
+                                    T, q_heads, kv_heads, head_dim, value_dim, page_size, _stream()),
+          "qkv_bias_store")
+    return q, k, v
+
+
+# --------------------------------------------------------------------------- fixed-size state mixers
+def _f32(shape, device) -> torch.Tensor:
+    return torch.empty(shape, dtype=torch.float32, device=device)
+
+
+def _column_ptr(t: torch.Tensor, column: int) -> ctypes.c_void_p:
+    return ctypes.c_void_p(t.data_ptr() + column * t.element_size())
+
+
+def retention_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, head_dim: int,
+                      value_dim: int, positions: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary: int,
+                      k_scale: float):
+    """From a fused projection [T, W] (q at column q_off, k at k_off, both [heads*d]; v at v_off
+    [heads*dv]): float32 q and k rotated on their first `rotary` dimensions (split-half, angle =
+    position * inv_freq), k times k_scale, and v widened. -> q, k [T,H,d], v [T,H,dv]."""
+    _check(proj, "proj", dims=2)
+    _check(positions, "positions", torch.int32, 1)
+    T = proj.shape[0]
+    if rotary:
+        _check(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.numel() != rotary // 2:
+            raise InvalidError("retention_prepare: inv_freq must have rotary/2 entries")
+    if max(q_off, k_off) + heads * head_dim > proj.shape[1] or v_off + heads * value_dim > proj.shape[1]:
+        raise InvalidError("retention_prepare: columns outside the projection")
+    q, k = _f32((T, heads, head_dim), proj.device), _f32((T, heads, head_dim), proj.device)
+    v = _f32((T, heads, value_dim), proj.device)
+    _done(_lib().lrm_retention_prepare(_ptr(proj), _code(proj.dtype), ctypes.c_longlong(proj.shape[1]), q_off, k_off,
+                                       v_off, _ptr(positions), _ptr(inv_freq if rotary else None), rotary,
+                                       ctypes.c_float(k_scale), _ptr(q), _ptr(k), _ptr(v), T, heads, head_dim,
+                                       value_dim, _stream()), "retention_prepare")
+    return q, k, v
+
+
+def delta_prepare(proj: torch.Tensor, conv_off: int, b_off: int, a: torch.Tensor, dt_bias: torch.Tensor,
+                  rate: torch.Tensor, taps: torch.Tensor, tails: torch.Tensor, cu_seqlens: torch.Tensor,
+                  seq_of_token: torch.Tensor, slots: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+                  value_dim: int, unit_eps: float, q_scale: float):
+    """Inputs of the gated delta rule from a fused projection [T, W]: the columns conv_off .. (q | k
+    | v channels) pass a short causal convolution (taps float32 [C, n]; inputs before the step come
+    from, and afterwards go to, `tails` float32 [slots, n-1, C]) and SiLU; q and k become unit
+    vectors per head (q also times q_scale); g = exp(-rate_h softplus(a + dt_bias)) per head and key
+    channel (a: the first H*d columns of a float32 [T, >= H*d] activation); b = sigmoid of the H
+    columns at b_off.
+    -> q, k [T,G,d], v [T,H,dv], g [T,H,d], b [T,H], all float32."""
+    _check(proj, "proj", dims=2)
+    T = proj.shape[0]
+    C = 2 * kv_heads * head_dim + heads * value_dim
+    _check(a, "a", torch.float32, 2)
+    _check(dt_bias, "dt_bias", torch.float32, 1)
+    _check(rate, "rate", torch.float32, 1)
+    _check(taps, "taps", torch.float32, 2)
+    _check(tails, "tails", torch.float32, 3)
+    n = taps.shape[1]
+    for name, t in (("cu_seqlens", cu_seqlens), ("seq_of_token", seq_of_token), ("slots", slots)):
+        _check(t, name, torch.int32, 1)
+    if (a.shape[0] != T or a.shape[1] < heads * head_dim or dt_bias.numel() != heads * head_dim or rate.numel() != heads
+            or taps.shape[0] != C or tuple(tails.shape[1:]) != (max(n - 1, 0), C)
+            or conv_off + C > proj.shape[1] or b_off + heads > proj.shape[1]):
+        raise InvalidError("delta_prepare: shapes do not agree")
+    dev = proj.device
+    q, k = _f32((T, kv_heads, head_dim), dev), _f32((T, kv_heads, head_dim), dev)
+    v, g, b = _f32((T, heads, value_dim), dev), _f32((T, heads, head_dim), dev), _f32((T, heads), dev)
+    _done(_lib().lrm_delta_prepare(_ptr(proj), _code(proj.dtype), ctypes.c_longlong(proj.shape[1]), conv_off, b_off,
+                                   _ptr(a), ctypes.c_longlong(a.shape[1]), _ptr(dt_bias), _ptr(rate), _ptr(taps), n, _ptr(tails), _ptr(cu_seqlens),
+                                   _ptr(seq_of_token), _ptr(slots), _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(b), T,
+                                   slots.numel(), heads, kv_heads, head_dim, value_dim, ctypes.c_float(unit_eps),
+                                   ctypes.c_float(q_scale), _stream()), "delta_prepare", launches=2 if n > 1 else 1)
+    return q, k, v, g, b
+
+
+def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor,
+                      cu_seqlens: torch.Tensor, slots: torch.Tensor, head_decay: Optional[torch.Tensor] = None,
+                      g: Optional[torch.Tensor] = None, beta: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Token-by-token update and read-out of a per-sequence, per-head matrix state (float32
+    [slots, H, d, dv], updated in place). With `head_decay` [H]: S <- a S + k v^T. With `g` [T,H,d]
+    and `beta` [T,H]: S <- diag(g) S, then S <- S + k (beta (v - S^T k))^T. o = S^T q after the
+    update. q, k float32 [T,KH,d] (query head h reads q/k head h // (H/KH)), v float32 [T,H,dv].
+    -> o float32 [T,H,dv]."""
+    for name, t, dims in (("q", q, 3), ("k", k, 3), ("v", v, 3), ("state", state, 4)):
+        _check(t, name, torch.float32, dims)
+    _check(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    _check(slots, "slots", torch.int32, 1)
+    T, KH, d = q.shape
+    H, dv = v.shape[1], v.shape[2]
+    if k.shape != q.shape or v.shape[0] != T or tuple(state.shape[1:]) != (H, d, dv) or H % KH:
+        raise InvalidError("linear_state_scan: shapes do not agree")
+    if (g is None) == (head_decay is None):
+        raise InvalidError("linear_state_scan: give either head_decay or g and beta")
+    if g is not None:
+        _check(g, "g", torch.float32, 3)
+        _check(beta, "beta", torch.float32, 2)
+        if tuple(g.shape) != (T, H, d) or tuple(beta.shape) != (T, H):
+            raise InvalidError("linear_state_scan: g must be [T,H,d] and beta [T,H]")
+    else:
+        _check(head_decay, "head_decay", torch.float32, 1)
+        if head_decay.numel() != H:
+            raise InvalidError("linear_state_scan: one decay per head")
+    out = _f32((T, H, dv), q.device)
+    _done(_lib().lrm_linear_state_scan(_ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(head_decay), _ptr(beta), _ptr(state),
+                                       _ptr(out), _ptr(cu_seqlens), _ptr(slots), slots.numel(), H, KH, d, dv,
+                                       _stream()), "linear_state_scan")
+    return out
+
+
+GATE_SILU, GATE_SIGMOID = 1, 2
+
+
+def head_norm_gate(o: torch.Tensor, eps: float, out_dtype: torch.dtype, weight: Optional[torch.Tensor] = None,
+                   gate: Optional[torch.Tensor] = None, gate_column: int = 0, gate_act: int = GATE_SILU,
+                   out_scale: float = 1.0) -> torch.Tensor:
+    """Per token and head: o / sqrt(mean(o^2) + eps) [* weight] [* act(gate)] * out_scale, o float32
+    [T,H,dv] -> [T, H*dv] in `out_dtype`. `gate` is a [T, W] activation whose columns gate_column ..
+    gate_column + H*dv hold the gate's pre-activation; act: GATE_SILU or GATE_SIGMOID."""
+    _check(o, "o", torch.float32, 3)
+    T, H, dv = o.shape
+    if weight is not None:
+        _check(weight, "weight", torch.float32, 1)
+        if weight.numel() != dv:
+            raise InvalidError("head_norm_gate: weight must have one entry per value dimension")
+    gate_ptr, stride = ctypes.c_void_p(0), 0
+    gate_code = _code(out_dtype)
+    if gate is not None:
+        _check(gate, "gate", dims=2)
+        gate_code = _code(gate.dtype)
+        if gate.shape[0] != T or gate_column + H * dv > gate.shape[1]:
+            raise InvalidError("head_norm_gate: gate columns outside the activation")
+        gate_ptr, stride = _column_ptr(gate, gate_column), gate.shape[1]
+    out = _activation(T, H * dv, out_dtype, o.device)
+    _done(_lib().lrm_head_norm_gate(_ptr(o), _ptr(weight), gate_ptr, gate_code, ctypes.c_longlong(stride), gate_act, _ptr(out),
+                                    _code(out_dtype), T, H, dv, ctypes.c_float(eps), ctypes.c_float(out_scale),
+                                    _stream()), "head_norm_gate")
+    return out
+
+
+# --------------------------------------------------------------------------- mixture of experts
+def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int):
+    """The `top` largest of each row of float32 logits [T, E] (+ bias [E]), lower index first on a
+    tie, and the softmax over the chosen ones. -> ids int32 [T, top], weights float32 [T, top]."""
+    _check(logits, "logits", torch.float32, 2)
+    T, E = logits.shape
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+        if bias.numel() != E:
+            raise InvalidError("moe_route: one bias per expert")
+    if not 0 < top <= E:
+        raise InvalidError("moe_route: top must be between 1 and the number of experts")
+    ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weights = _f32((T, top), logits.device)
+    _done(_lib().lrm_moe_route(_ptr(logits), _ptr(bias), _ptr(ids), _ptr(weights), T, E, top, _stream()), "moe_route")
+    return ids, weights
+
+
+def moe_experts_rows(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor,
+                     weights: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """Every token's chosen experts, token by token: planes float32 [n, T, width] whose sum in plane
+    order is sum_c weights[t,c] * expert_ids[t,c](x[t]). gate, up [E, ff, width], down [E, width, ff]."""
+    _check(x, "x", dims=2)
+    T, width = x.shape
+    E, ff = gate.shape[0], gate.shape[1]
+    for name, t, shape in (("gate", gate, (E, ff, width)), ("up", up, (E, ff, width)), ("down", down, (E, width, ff))):
+        _check(t, name, gate.dtype, 3)
+        if tuple(t.shape) != shape:
+            raise InvalidError(f"moe_experts_rows: {name} must be {list(shape)}")
+    _check(ids, "ids", torch.int32, 2)
+    _check(weights, "weights", torch.float32, 2)
+    top = ids.shape[1]
+    if ids.shape[0] != T or tuple(weights.shape) != (T, top):
+        raise InvalidError("moe_experts_rows: one row of choices per token")
+    if T > 65535:
+        raise UnsupportedError("moe_experts_rows: more than 65535 tokens in one step")
+    lib = _lib()
+    slices = int(lib.lrm_moe_rows_slices(T, top, ff))
+    planes = _f32((top * slices, T, width), x.device)
+    _done(lib.lrm_moe_experts_rows(_ptr(x), _code(x.dtype), _ptr(gate), _ptr(up), _ptr(down), _code(gate.dtype),
+                                   _ptr(ids), _ptr(weights), _ptr(planes), T, width, ff, top, slices,
+                                   ctypes.c_float(limit), ctypes.c_float(alpha), _stream()), "moe_experts_rows")
+    return planes
+
+
+def add_row_(x: torch.Tensor, row: torch.Tensor) -> torch.Tensor:
+    """x[t, :] += row for every row t; both float32."""
+    _check(x, "x", torch.float32, 2)
+    _check(row, "row", torch.float32, 1)
+    if row.numel() != x.shape[1]:
+        raise InvalidError("add_row_: the row must be as wide as x")
+    _done(_lib().lrm_add_row(_ptr(x), _ptr(row), ctypes.c_longlong(x.shape[0]), x.shape[1], _stream()), "add_row_")
+    return x
+
+
 # --------------------------------------------------------------------------- attention
+def _check_slopes(slopes: Optional[torch.Tensor], heads: int) -> None:
+    if slopes is not None:
+        _check(slopes, "slopes", torch.float32, 1)
+        if slopes.numel() != heads:
+            raise InvalidError("one distance slope per query head")
+
+
 def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor,
                       seq_of_token: torch.Tensor, max_seq_len: int, scale: float,
-                      window: Optional[int] = None) -> torch.Tensor:
-    """Causal GQA over the step's own packed k, v (sequences start at position 0). -> [T, Hq*d]"""
+                      window: Optional[int] = None, slopes: Optional[torch.Tensor] = None,
+                      out_scale: float = 1.0) -> torch.Tensor:
+    """Causal GQA over the step's own packed k, v (sequences start at position 0). -> [T, Hq*dv]
+    (v may have another head width dv than q and k). `slopes` (float32 [Hq]): a key n positions
+    behind the query loses slopes[h] * n from its score. `out_scale` multiplies the result."""
     _check(q, "q", dims=3)
     _check(k, "k", q.dtype, 3)
     _check(v, "v", q.dtype, 3)
@@ -336,17 +573,24 @@ def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seql
     _check(seq_of_token, "seq_of_token", torch.int32, 1)
     T, Hq, d = q.shape
     Hk = k.shape[1]
-    if k.shape != v.shape or k.shape[0] != T or k.shape[2] != d or Hq % Hk:
+    if k.shape[:2] != v.shape[:2] or k.shape[0] != T or k.shape[2] != d or Hq % Hk:
         raise InvalidError("attention_prefill: q, k, v shapes do not agree")
-    out = _activation(T, Hq * d, q.dtype, q.device)
+    _check_slopes(slopes, Hq)
+    out = _activation(T, Hq * v.shape[2], q.dtype, q.device)
     from . import attention_dispatch
-    attention_dispatch.prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len, scale, window or 0)
+    attention_dispatch.prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len, scale, window or 0,
+                               slopes, out_scale)
     return out
 
 
+def _value_dim(kv) -> int:
+    return kv.v.shape[3]
+
+
 def attention_decode(q: torch.Tensor, kv, slots: torch.Tensor, kv_lens: torch.Tensor,
-                     max_kv_len: int, scale: float, window: Optional[int] = None) -> torch.Tensor:
-    """One query per sequence over its cached keys (the newest already stored). -> [B, Hq*d]"""
+                     max_kv_len: int, scale: float, window: Optional[int] = None,
+                     slopes: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> torch.Tensor:
+    """One query per sequence over its cached keys (the newest already stored). -> [B, Hq*dv]"""
     _check(q, "q", dims=3)
     _check(kv.k, "k pages", q.dtype, 4)
     _check(kv.v, "v pages", q.dtype, 4)
@@ -356,15 +600,17 @@ def attention_decode(q: torch.Tensor, kv, slots: torch.Tensor, kv_lens: torch.Te
     B, Hq, d = q.shape
     if tuple(kv.k.shape[1:]) != (kv.kv_heads, kv.page_size, d) or Hq % kv.kv_heads:
         raise InvalidError("attention_decode: cache pages do not match the query geometry")
-    out = _activation(B, Hq * d, q.dtype, q.device)
+    _check_slopes(slopes, Hq)
+    out = _activation(B, Hq * _value_dim(kv), q.dtype, q.device)
     from . import attention_dispatch
-    attention_dispatch.decode(q, kv, out, slots, kv_lens, max_kv_len, scale, window or 0)
+    attention_dispatch.decode(q, kv, out, slots, kv_lens, max_kv_len, scale, window or 0, slopes, out_scale)
     return out
 
 
 def attention_extend(q: torch.Tensor, kv, cu_seqlens: torch.Tensor, seq_of_token: torch.Tensor,
                      positions: torch.Tensor, slots: torch.Tensor, kv_lens: torch.Tensor, max_seq_len: int,
-                     scale: float, window: Optional[int] = None) -> torch.Tensor:
+                     scale: float, window: Optional[int] = None, slopes: Optional[torch.Tensor] = None,
+                     out_scale: float = 1.0) -> torch.Tensor:
     """Several queries per sequence over the cache, which already holds the step's own keys:
     query t (packed, of sequence seq_of_token[t]) sees the keys up to positions[t]. -> [T, Hq*d]"""
     _check(q, "q", dims=3)
@@ -380,10 +626,11 @@ def attention_extend(q: torch.Tensor, kv, cu_seqlens: torch.Tensor, seq_of_token
             raise InvalidError(f"attention_extend: {name} must have {n} entries")
     if tuple(kv.k.shape[1:]) != (kv.kv_heads, kv.page_size, d) or Hq % kv.kv_heads:
         raise InvalidError("attention_extend: cache pages do not match the query geometry")
-    out = _activation(T, Hq * d, q.dtype, q.device)
+    _check_slopes(slopes, Hq)
+    out = _activation(T, Hq * _value_dim(kv), q.dtype, q.device)
     from . import attention_dispatch
     attention_dispatch.extend(q, kv, out, cu_seqlens, seq_of_token, positions, slots, kv_lens, max_seq_len,
-                              scale, window or 0)
+                              scale, window or 0, slopes, out_scale)
     return out
 
 

@@ -1,12 +1,16 @@
-from .base import (Block, FeedForward, KeyValueRequest, LayerSpec, Mixer, ModelPlan, Norm, Part,
-                   PartSpec, PositionEncoding, ScheduleEntry, StateRequest)
+from .base import (Block, CompositeRequest, FeedForward, KeyValueRequest, LayerSpec, Mixer, ModelPlan, Norm,
+                   Part, PartSpec, PositionEncoding, ScheduleEntry, StateRequest)
 from .linear import LinearWeight
 from .norm import RMSNorm
-from .rope import RotaryEmbedding
+from .rope import DistancePenalty, RotaryEmbedding
 from .attention import Attention
 from .mlp import GatedMLP
-from .block import PreNormBlock
+from .recurrent import GatedDeltaRule, Retention
+from .parallel import ParallelMixer
+from .moe import MixtureOfExperts
+from .block import PreNormBlock, PreNormMixerBlock
 
-__all__ = ["Block", "FeedForward", "KeyValueRequest", "LayerSpec", "Mixer", "ModelPlan", "Norm",
+__all__ = ["Block", "CompositeRequest", "FeedForward", "KeyValueRequest", "LayerSpec", "Mixer", "ModelPlan", "Norm",
            "Part", "PartSpec", "PositionEncoding", "ScheduleEntry", "StateRequest", "LinearWeight",
-           "RMSNorm", "RotaryEmbedding", "Attention", "GatedMLP", "PreNormBlock"]
+           "RMSNorm", "RotaryEmbedding", "DistancePenalty", "Attention", "GatedMLP", "Retention", "GatedDeltaRule",
+           "ParallelMixer", "MixtureOfExperts", "PreNormBlock", "PreNormMixerBlock"]

@@ -25,15 +25,25 @@ class Attention(Mixer):
     cache. `window` limits a query to the last `window` keys. Which kernels run
     is decided in kernels/attention_dispatch.py (`attend`); a variant mixer
     overrides `before_rotation` to transform q and k per head.
+
+    Options: `value_dim`, the head width of values when it is not that of queries and keys;
+    `bias`, the q, k and v projections have biases (added in float32 before rounding);
+    `output_scale`, a factor on the mixer's output (a mixer that enters a weighted sum of
+    mixers), applied to the mixed heads before the output projection. A position scheme that
+    is a linear distance penalty (`distance_slopes`) is applied by the attention kernels.
     """
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: Optional[PartSpec] = None, window: Optional[int] = None,
-                 scale: Optional[float] = None):
+                 scale: Optional[float] = None, value_dim: Optional[int] = None, bias: bool = False,
+                 output_scale: float = 1.0):
         if num_heads <= 0 or num_kv_heads <= 0 or num_heads % num_kv_heads:
             raise InvalidError("attention heads must be a multiple of key/value heads")
         self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
         self.head_dim, self.window = head_dim, window
+        self.value_dim = head_dim if value_dim is None else int(value_dim)
+        self.has_bias, self.output_scale = bool(bias), float(output_scale)
+        self.bias: Optional[torch.Tensor] = None
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.position = build_part(POSITION_ENCODINGS, position, "position encoding") \
             if position is not None else None
@@ -47,8 +57,12 @@ class Attention(Mixer):
 
     def tensors(self) -> Dict[str, TensorSpec]:
         q, kv, h = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim, self.hidden_size
+        v, mixed = self.num_kv_heads * self.value_dim, self.num_heads * self.value_dim
         out = {"q_proj.weight": TensorSpec((q, h)), "k_proj.weight": TensorSpec((kv, h)),
-               "v_proj.weight": TensorSpec((kv, h)), "o_proj.weight": TensorSpec((h, q))}
+               "v_proj.weight": TensorSpec((v, h)), "o_proj.weight": TensorSpec((h, mixed))}
+        if self.has_bias:
+            out.update({"q_proj.bias": TensorSpec((q,)), "k_proj.bias": TensorSpec((kv,)),
+                        "v_proj.bias": TensorSpec((v,))})
         if self.position is not None:
             out.update({"position." + n: s for n, s in self.position.tensors().items()})
         return out
@@ -68,17 +82,36 @@ class Attention(Mixer):
         self.qkv = LinearWeight(fused)
         self.q_only = LinearWeight(fused[: self.num_heads * self.head_dim])
         self.out = LinearWeight(weights["o_proj.weight"])
+        if self.has_bias:
+            if order is not None:
+                raise InvalidError("projection biases with a reordered head are not built")
+            self.bias = torch.cat([weights["q_proj.bias"], weights["k_proj.bias"], weights["v_proj.bias"]]) \
+                .to(torch.float32).contiguous()
         if self.position is not None:
             self.position.bind({n[len("position."):]: t for n, t in weights.items()
                                 if n.startswith("position.")}, runtime)
 
     def cache_request(self):
-        return KeyValueRequest(self.num_kv_heads, self.head_dim, self.window)
+        return KeyValueRequest(self.num_kv_heads, self.head_dim, self.window,
+                               None if self.value_dim == self.head_dim else self.value_dim)
 
     def forward(self, x, ctx, cache, residual):
         entry = ctx.entry
         weight = self.qkv if entry.writes_cache else self.q_only
         rotary = self.position.rotary_table() if self.position is not None else None
+        slopes = self.position.distance_slopes() if self.position is not None else None
+        if self.has_bias or self.value_dim != self.head_dim or slopes is not None or self.output_scale != 1.0:
+            # the general form: projection, then a split that adds the biases and stores keys and
+            # values, then the attention kernels that know the penalty and the value width
+            bias = self.bias
+            if bias is not None and not entry.writes_cache:
+                bias = bias[: self.num_heads * self.head_dim]
+            mixed = ops.attend(weight(x), q_heads=self.num_heads, kv_heads=self.num_kv_heads,
+                               head_dim=self.head_dim, rotary=rotary, ctx=ctx, cache=cache,
+                               writes_cache=entry.writes_cache, cache_entry=entry.cache, scale=self.scale,
+                               window=self.window, value_dim=self.value_dim, bias=bias, slopes=slopes,
+                               out_scale=self.output_scale)
+            return self.out(mixed, epilogue=ops.ADD, out=residual, ctx=ctx)
         # Nothing stands between projection and rotation unless a variant mixer overrides the hook
         # or the position scheme is no rotary table: the kernels may then do both in one launch.
         direct = (type(self).before_rotation is Attention.before_rotation

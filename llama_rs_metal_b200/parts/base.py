@@ -82,6 +82,9 @@ class ScheduleEntry:
     layer: int
     cache: int
     writes_cache: bool = True
+    # row of the plan's `stream_offsets` table that is added to the residual stream right before
+    # this entry runs (None: nothing is added)
+    add_offset: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -98,6 +101,9 @@ class ModelPlan:
     stop_token_ids: Tuple[int, ...] = ()
     embedding_scale: Optional[float] = None  # embedded rows are multiplied by this (None: 1)
     logit_scale: Optional[float] = None      # logits are multiplied by this (None: 1)
+    # (checkpoint name, rows) of a [rows, hidden] table of vectors that schedule entries add to
+    # the residual stream (ScheduleEntry.add_offset), or None
+    stream_offsets: Optional[Tuple[str, int]] = None
 
 
 # --------------------------------------------------------------------------- cache requests
@@ -106,12 +112,14 @@ class KeyValueRequest:
     """A mixer whose memory grows with the sequence: keys and values per token.
 
     `window` None keeps every key; a number keeps the last `window` positions.
-    Layers with equal requests share one storage group.
+    `value_dim` None: values are as wide as keys. Layers with equal requests share
+    one storage group.
     """
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -120,6 +128,16 @@ class StateRequest:
 
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class CompositeRequest:
+    """A mixer that keeps several things per sequence (keys and values beside a state, a state
+    beside the tail of a convolution, two mixers side by side): one request per thing, each a
+    KeyValueRequest, a StateRequest, None, or again a CompositeRequest. The mixer gets a tuple
+    of views in the same order (and of the same nesting)."""
+
+    parts: Tuple[Any, ...]
 
 
 # --------------------------------------------------------------------------- part interfaces
@@ -164,6 +182,12 @@ class PositionEncoding(Part):
         queries and keys are reordered alike."""
         return None
 
+    def distance_slopes(self) -> Optional[torch.Tensor]:
+        """float32 [query heads] when the scheme is a penalty on the score that grows linearly
+        with the distance between query and key (slope per head), which the attention kernels
+        apply themselves; None for every other scheme."""
+        return None
+
     def apply(self, q: torch.Tensor, k: torch.Tensor, ctx) -> Tuple[torch.Tensor, torch.Tensor]:
         """Any scheme that is not a rotary table transforms q and k here."""
         return q, k
@@ -171,7 +195,7 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     def cache_request(self):
-        """KeyValueRequest, StateRequest or None."""
+        """KeyValueRequest, StateRequest, CompositeRequest or None."""
         return None
 
     def forward(self, x: torch.Tensor, ctx, cache, residual: torch.Tensor) -> torch.Tensor:

@@ -29,3 +29,23 @@ class PreNormBlock(Block):
         hidden = self.feed_forward.forward(x, ctx, residual=hidden)
         ctx.may_defer = False
         return hidden
+
+
+@register_block("pre_norm_mixer")
+class PreNormMixerBlock(Block):
+    """hidden += mixer(norm(hidden)): a layer without a feed-forward."""
+
+    graph_safe = True
+    roles = {"mixer": "mixer", "mixer_norm": "norm"}
+
+    @property
+    def folds_pending_on_entry(self) -> bool:
+        return self.mixer_norm.folds_pending
+
+    def forward(self, hidden, ctx, cache):
+        after = ctx.next_folds_pending
+        x = self.mixer_norm.forward(hidden, ctx)
+        ctx.may_defer = after
+        hidden = self.mixer.forward(x, ctx, cache, residual=hidden)
+        ctx.may_defer = False
+        return hidden

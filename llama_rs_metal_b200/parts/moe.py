@@ -1,0 +1,71 @@
+"""Mixture of experts: a router picks a few small gated feed-forwards per token."""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..errors import InvalidError, UnsupportedError
+from ..kernels import ops
+from ..registry import register_feed_forward
+from ..weights.loader import TensorSpec
+from .base import FeedForward
+from .linear import LinearWeight
+
+
+@register_feed_forward("moe")
+class MixtureOfExperts(FeedForward):
+    """z = W_r x (+ b_r) in float32; the `top` experts with the largest z are chosen and weighted
+    by the softmax over the chosen z only; the output is the weighted sum of their outputs,
+    added to the residual stream.
+
+    An expert (activation "clamped_gate"): g = min(W_gate x, limit), u = clamp(W_up x, -limit,
+    limit), y = g sigmoid(alpha g) (u + 1), output W_down y; no biases.
+
+    The router's matrix is kept in float32 whatever the runtime, so its product runs on the
+    float32 kernel. The experts' matrices are stacked [experts, ...] so one launch serves every
+    choice; the choices' outputs come back as float32 planes that are added to the stream in a
+    fixed order (by the next norm where it folds them)."""
+
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top: int,
+                 activation: str = "clamped_gate", limit: float = 7.0, alpha: float = 1.702,
+                 router_bias: bool = True):
+        if activation != "clamped_gate":
+            raise UnsupportedError(f"expert activation {activation!r}")
+        if num_experts <= 0 or not 0 < top <= num_experts:
+            raise InvalidError("the router chooses between 1 and all of the experts")
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.num_experts, self.top = num_experts, top
+        self.limit, self.alpha, self.router_bias = float(limit), float(alpha), bool(router_bias)
+        self.router: Optional[LinearWeight] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        h, f = self.hidden_size, self.intermediate_size
+        out = {"router.weight": TensorSpec((self.num_experts, h))}
+        if self.router_bias:
+            out["router.bias"] = TensorSpec((self.num_experts,))
+        for e in range(self.num_experts):
+            out[f"experts.{e}.gate_proj.weight"] = TensorSpec((f, h))
+            out[f"experts.{e}.up_proj.weight"] = TensorSpec((f, h))
+            out[f"experts.{e}.down_proj.weight"] = TensorSpec((h, f))
+        return out
+
+    def bind(self, weights, runtime) -> None:
+        self.router = LinearWeight(weights["router.weight"].to(torch.float32))
+        self.bias = weights["router.bias"].to(torch.float32).contiguous() if self.router_bias else None
+        stack = lambda name: torch.stack([weights[f"experts.{e}.{name}.weight"]  # noqa: E731
+                                          for e in range(self.num_experts)]).contiguous()
+        self.gate, self.up, self.down = stack("gate_proj"), stack("up_proj"), stack("down_proj")
+
+    def forward(self, x, ctx, residual):
+        logits = self.router(x, out_dtype=torch.float32)
+        ids, weights = ops.moe_route(logits, self.bias, self.top)
+        planes = ops.moe_experts_rows(x, self.gate, self.up, self.down, ids, weights, self.limit, self.alpha)
+        if ctx.may_defer:
+            ctx.settle(residual)  # at most one set of partial sums is pending at a time
+            ctx.pending = planes
+            return residual
+        return ops.add_planes_(residual, planes)

@@ -13,22 +13,28 @@ from .base import Norm
 
 @register_norm("rms_norm")
 class RMSNorm(Norm):
-    """y = x / sqrt(mean(x^2) + eps) * w, statistics in float32
-    (crates/metal-backend/src/shaders/elementwise.metal:31-46; no +1 offset for Llama)."""
+    """y = x / sqrt(mean(x^2) + eps) * (offset + w), statistics in float32
+    (crates/metal-backend/src/shaders/elementwise.metal:31-46; no +1 offset for Llama).
+    `offset` 1 is for weights stored around zero; the sum is made once, in float32, when the
+    weights are bound."""
 
     graph_safe = True
     folds_pending = True
 
-    def __init__(self, size: int, eps: float):
+    def __init__(self, size: int, eps: float, offset: float = 0.0):
         self.size = size
         self.eps = float(eps)
+        self.offset = float(offset)
         self.weight: Optional[torch.Tensor] = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
         return {"weight": TensorSpec((self.size,))}
 
     def bind(self, weights, runtime) -> None:
-        self.weight = weights["weight"].contiguous()
+        weight = weights["weight"]
+        if self.offset != 0.0:
+            weight = weight.to(torch.float32) + self.offset
+        self.weight = weight.contiguous()
 
     def forward(self, hidden, ctx, rows=None):
         # partial sums a product left for the residual stream are added in the same pass

@@ -1,0 +1,174 @@
+"""Mixers whose memory is a matrix of fixed size per sequence and head.
+
+Both keep S [head_dim, value_dim] in float32 per (sequence, head) in the cache's state storage,
+update it token by token and read it out with the query (csrc/recurrent_scan.cu):
+
+* `retention`: S <- a_h S + k v^T with one fixed decay a_h per head, no softmax and no
+  denominator; rotary positions on q and k; the read-out is normalized per head and gated.
+* `gated_delta_rule`: S <- diag(g) S; S <- S + k (b (v - S^T k))^T with decays g per key channel
+  and step sizes b computed from the input; q, k, v pass a short causal convolution first.
+
+A step of any size (a prompt, a portion, one token) runs the same scan from the state the
+steps before left, so nothing depends on how a sequence was cut into steps.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Sequence
+
+import torch
+
+from ..errors import InvalidError, UnsupportedError
+from ..kernels import ops
+from ..registry import POSITION_ENCODINGS, build_part, register_mixer
+from ..weights.loader import TensorSpec
+from .base import CompositeRequest, Mixer, PartSpec, StateRequest
+from .linear import LinearWeight
+
+
+def _needs_own_state(ctx) -> None:
+    if not ctx.entry.writes_cache:
+        raise UnsupportedError("a mixer with a fixed-size state cannot read another layer's state")
+
+
+@register_mixer("retention")
+class Retention(Mixer):
+    """o_t = S_t^T q_t, S_t = a_h S_(t-1) + k_t v_t^T per head, with q and k rotated by position
+    (`position`: a rotary PartSpec, or None) and k multiplied by `key_scale` (default
+    head_dim^-1/2) after the rotation. Each head's o is divided by its root mean square
+    (`eps`, no weight), the heads are concatenated, multiplied by silu(W_g x) and projected."""
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, value_dim: int, decay: Sequence[float],
+                 eps: float, position: Optional[PartSpec] = None, key_scale: Optional[float] = None,
+                 output_scale: float = 1.0):
+        if num_heads <= 0 or head_dim <= 0 or value_dim <= 0 or len(decay) != num_heads:
+            raise InvalidError("retention needs one decay per head")
+        self.hidden_size, self.num_heads, self.head_dim, self.value_dim = hidden_size, num_heads, head_dim, value_dim
+        self.decay = [float(a) for a in decay]
+        self.eps, self.output_scale = float(eps), float(output_scale)
+        self.key_scale = float(key_scale) if key_scale is not None else head_dim ** -0.5
+        self.position = build_part(POSITION_ENCODINGS, position, "position encoding") \
+            if position is not None else None
+        self.fused: Optional[LinearWeight] = None
+        self.out: Optional[LinearWeight] = None
+        self.head_decay: Optional[torch.Tensor] = None
+
+    @property
+    def graph_safe(self) -> bool:
+        return self.position is None or self.position.graph_safe
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        qk, v, h = self.num_heads * self.head_dim, self.num_heads * self.value_dim, self.hidden_size
+        return {"q_proj.weight": TensorSpec((qk, h)), "k_proj.weight": TensorSpec((qk, h)),
+                "v_proj.weight": TensorSpec((v, h)), "g_proj.weight": TensorSpec((v, h)),
+                "o_proj.weight": TensorSpec((h, v))}
+
+    def bind(self, weights, runtime) -> None:
+        # one matrix q | k | v | g: each output is the same dot product as with separate matrices
+        self.fused = LinearWeight(torch.cat([weights["q_proj.weight"], weights["k_proj.weight"],
+                                             weights["v_proj.weight"], weights["g_proj.weight"]], dim=0))
+        self.out = LinearWeight(weights["o_proj.weight"])
+        self.head_decay = torch.tensor(self.decay, dtype=torch.float64).to(torch.float32).to(runtime.device)
+        if self.position is not None:
+            self.position.bind({}, runtime)
+            if self.position.rotary_table() is None:
+                raise UnsupportedError("retention rotates q and k by a rotary table or not at all")
+
+    def cache_request(self):
+        return StateRequest((self.num_heads, self.head_dim, self.value_dim), torch.float32)
+
+    def forward(self, x, ctx, cache, residual):
+        _needs_own_state(ctx)
+        H, d, dv = self.num_heads, self.head_dim, self.value_dim
+        projected = self.fused(x)
+        inv_freq, rotary = self.position.rotary_table() if self.position is not None else (None, 0)
+        q, k, v = ops.retention_prepare(projected, 0, H * d, 2 * H * d, H, d, dv, ctx.positions, inv_freq, rotary,
+                                        self.key_scale)
+        o = ops.linear_state_scan(q, k, v, cache.state, ctx.cu_seqlens, ctx.slots, head_decay=self.head_decay)
+        mixed = ops.head_norm_gate(o, self.eps, projected.dtype, gate=projected, gate_column=2 * H * d + H * dv,
+                                   gate_act=ops.GATE_SILU, out_scale=self.output_scale)
+        return self.out(mixed, epilogue=ops.ADD, out=residual, ctx=ctx)
+
+
+@register_mixer("gated_delta_rule")
+class GatedDeltaRule(Mixer):
+    """q = W_q x, k = W_k x (kv_heads x head_dim), v = W_v x (heads x value_dim); each passes a
+    causal convolution of `conv_taps` taps per channel (no bias, zeros before the start) and SiLU;
+    q and k become unit vectors per head (x / sqrt(sum x^2 + unit_eps)), q times head_dim^-1/2.
+    b = sigmoid(W_b x) per head; g = exp(-exp(A_log_h) softplus(W_a2 (W_a1 x) + dt_bias)) per head
+    and key channel. Per head, with q/k head h // (heads / kv_heads):
+        S <- diag(g) S;  u = b (v - S^T k);  S <- S + k u^T;  o = S^T q.
+    o is divided by its root mean square over value_dim (`eps`), multiplied by a weight shared by
+    the heads and by sigmoid(W_g2 (W_g1 x)), then projected. The inner ranks of the two low-rank
+    products are the checkpoint's (`decay_rank`, `gate_rank` None) unless given.
+    State: S in float32 and the last conv_taps - 1 convolution inputs of every channel."""
+
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
+                 conv_taps: int, eps: float, decay_rank: Optional[int] = None, gate_rank: Optional[int] = None,
+                 unit_eps: float = 1e-6, output_scale: float = 1.0):
+        if num_heads <= 0 or num_kv_heads <= 0 or num_heads % num_kv_heads or conv_taps <= 0:
+            raise InvalidError("gated delta rule: heads must be a multiple of key heads, and taps positive")
+        self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
+        self.head_dim, self.value_dim, self.conv_taps = head_dim, value_dim, conv_taps
+        self.decay_rank, self.gate_rank = decay_rank, gate_rank
+        self.eps, self.unit_eps, self.output_scale = float(eps), float(unit_eps), float(output_scale)
+        self.channels = 2 * num_kv_heads * head_dim + num_heads * value_dim
+        self.fused: Optional[LinearWeight] = None
+        self.low: Optional[LinearWeight] = None
+        self.high: Optional[LinearWeight] = None
+        self.out: Optional[LinearWeight] = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        H, G, d, dv, h, n = (self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, self.hidden_size,
+                             self.conv_taps)
+        return {"q_proj.weight": TensorSpec((G * d, h)), "k_proj.weight": TensorSpec((G * d, h)),
+                "v_proj.weight": TensorSpec((H * dv, h)), "q_conv.weight": TensorSpec((G * d, n)),
+                "k_conv.weight": TensorSpec((G * d, n)), "v_conv.weight": TensorSpec((H * dv, n)),
+                "b_proj.weight": TensorSpec((H, h)), "A_log": TensorSpec((H,)), "dt_bias": TensorSpec((H * d,)),
+                "a_down.weight": TensorSpec((self.decay_rank, h)), "a_up.weight": TensorSpec((H * d, self.decay_rank)),
+                "g_down.weight": TensorSpec((self.gate_rank, h)), "g_up.weight": TensorSpec((H * dv, self.gate_rank)),
+                "norm.weight": TensorSpec((dv,)), "o_proj.weight": TensorSpec((h, H * dv))}
+
+    def bind(self, weights, runtime) -> None:
+        H, d, dv = self.num_heads, self.head_dim, self.value_dim
+        a_down, a_up, g_down, g_up = (weights[n + ".weight"] for n in ("a_down", "a_up", "g_down", "g_up"))
+        ra, rg = a_down.shape[0], g_down.shape[0]
+        if a_up.shape[1] != ra or g_up.shape[1] != rg:
+            raise InvalidError("gated delta rule: the two halves of a low-rank product disagree on its rank")
+        # q | k | v | b in one product; the two low-rank products share a first product
+        # [a_down; g_down] and a second one with the block matrix [[a_up, 0], [0, g_up]]: the zero
+        # blocks add exact zeros, so every output is the sum it would be with separate matrices
+        self.fused = LinearWeight(torch.cat([weights["q_proj.weight"], weights["k_proj.weight"],
+                                             weights["v_proj.weight"], weights["b_proj.weight"]], dim=0))
+        self.low = LinearWeight(torch.cat([a_down, g_down], dim=0))
+        high = torch.zeros((H * d + H * dv, ra + rg), dtype=a_up.dtype, device=a_up.device)
+        high[: H * d, :ra] = a_up
+        high[H * d:, ra:] = g_up
+        self.high = LinearWeight(high)
+        self.out = LinearWeight(weights["o_proj.weight"])
+        f32 = torch.float32
+        self.taps = torch.cat([weights["q_conv.weight"], weights["k_conv.weight"], weights["v_conv.weight"]],
+                              dim=0).to(f32).contiguous()
+        self.rate = torch.exp(weights["A_log"].to(f32)).contiguous()      # exp(A_log), float32
+        self.dt_bias = weights["dt_bias"].to(f32).contiguous()
+        self.norm_weight = weights["norm.weight"].to(f32).contiguous()
+
+    def cache_request(self):
+        return CompositeRequest((
+            StateRequest((self.num_heads, self.head_dim, self.value_dim), torch.float32),
+            StateRequest((self.conv_taps - 1, self.channels), torch.float32)))
+
+    def forward(self, x, ctx, cache, residual):
+        _needs_own_state(ctx)
+        H, G, d, dv = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim
+        state, tails = cache
+        projected = self.fused(x)                                        # [T, q | k | v | b]
+        both = self.high(self.low(x), out_dtype=torch.float32)           # [T, a (H d) | gate (H dv)], float32
+        q, k, v, g, beta = ops.delta_prepare(projected, 0, self.channels, both, self.dt_bias, self.rate, self.taps,
+                                             tails.state, ctx.cu_seqlens, ctx.seq_of_token, ctx.slots, H, G, d, dv,
+                                             self.unit_eps, d ** -0.5)
+        o = ops.linear_state_scan(q, k, v, state.state, ctx.cu_seqlens, ctx.slots, g=g, beta=beta)
+        mixed = ops.head_norm_gate(o, self.eps, projected.dtype, weight=self.norm_weight, gate=both,
+                                   gate_column=H * d, gate_act=ops.GATE_SIGMOID, out_scale=self.output_scale)
+        return self.out(mixed, epilogue=ops.ADD, out=residual, ctx=ctx)

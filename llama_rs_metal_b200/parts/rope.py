@@ -88,3 +88,28 @@ class RotaryEmbedding(PositionEncoding):
 
     def rotary_table(self) -> Optional[Tuple[torch.Tensor, int]]:
         return self.inv_freq, self.rotary_dim
+
+
+@register_position_encoding("distance_penalty")
+class DistancePenalty(PositionEncoding):
+    """No rotation: a key n positions behind its query loses slope_h * n from its score, with
+    slope_h = 2^(-span (h + 1) / heads) for query head h = 0 .. heads - 1 (`span` 8 gives slopes
+    from 2^(-8/heads) down to 2^-8). The slopes are made once, in double precision, and rounded
+    to float32; the attention kernels subtract slope * float(distance) from the scaled score."""
+
+    graph_safe = True
+
+    def __init__(self, num_heads: int, span: float = 8.0):
+        if num_heads <= 0 or span <= 0:
+            raise InvalidError("a distance penalty needs heads and a positive span")
+        self.num_heads, self.span = int(num_heads), float(span)
+        self.slopes: Optional[torch.Tensor] = None
+
+    def slope_values(self) -> List[float]:
+        return [2.0 ** (-self.span * (h + 1) / self.num_heads) for h in range(self.num_heads)]
+
+    def bind(self, weights, runtime) -> None:
+        self.slopes = torch.tensor(self.slope_values(), dtype=torch.float64).to(torch.float32).to(runtime.device)
+
+    def distance_slopes(self) -> Optional[torch.Tensor]:
+        return self.slopes

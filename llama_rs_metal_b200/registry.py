@@ -68,11 +68,14 @@ def register_block(kind: str):
 def find_architecture(root: Mapping[str, Any]) -> Architecture:
     """The registered architecture a config.json names.
 
-    `architectures[0]` is looked up first; the reference keys on `model_type`
-    (crates/model-format/src/mlx/config.rs:28-44), which is the second try.
+    `architectures[0]` (or a single name under `architecture`) is looked up first; the
+    reference keys on `model_type` (crates/model-format/src/mlx/config.rs:28-44), which is the
+    second try.
     """
     _ensure_builtin()
     archs = root.get("architectures")
+    if not isinstance(archs, list) and isinstance(root.get("architecture"), str):
+        archs = [root["architecture"]]
     if isinstance(archs, list):
         for name in archs:
             if name in ARCHITECTURES:

@@ -21,7 +21,7 @@ crates/model-format/src/checkpoint.rs:252-265).
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, Iterable, Mapping, Tuple
+from typing import Dict, Iterable, Mapping, Optional, Tuple
 
 import torch
 
@@ -33,10 +33,16 @@ PREFIXES = ("model.language_model.", "language_model.")  # mlx/names.rs:3-8
 
 @dataclass(frozen=True)
 class TensorSpec:
-    """What a part expects of one tensor."""
+    """What a part expects of one tensor. A dimension given as None is the checkpoint's to
+    choose (an inner rank that no configuration key names): the part reads it off the tensor
+    when it is bound."""
 
-    shape: Tuple[int, ...]
+    shape: Tuple[Optional[int], ...]
     kind: str = "float"  # "float" | "integer"
+
+    def fits(self, found) -> bool:
+        found = tuple(found)
+        return len(found) == len(self.shape) and all(w is None or w == f for w, f in zip(self.shape, found))
 
 
 def canonical_name(name: str) -> str:
@@ -63,7 +69,7 @@ def check_names_and_shapes(found: Mapping[str, Tuple[int, ...]], wanted: Mapping
     missing = [n for n in wanted if n not in found]
     unexpected = [n for n in found if n not in wanted and n not in ignored]
     wrong = [(n, wanted[n].shape, found[n]) for n in wanted
-             if n in found and tuple(found[n]) != tuple(wanted[n].shape)]
+             if n in found and not wanted[n].fits(found[n])]
     if missing or wrong or (strict and unexpected):
         raise WeightError(missing=missing, unexpected=unexpected, wrong_shape=wrong)
     return tuple(sorted(unexpected))

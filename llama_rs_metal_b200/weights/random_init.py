@@ -35,6 +35,8 @@ def random_tensors(wanted: Mapping[str, TensorSpec], seed: int, std: float = 0.0
     folder written on the CPU and a model drawn on the device are different random models."""
     out = {}
     for name, spec in wanted.items():
+        if any(n is None for n in spec.shape):
+            raise ValueError(f"{name}: a dimension is left to the checkpoint; random weights need it in the configuration")
         gen = _generator(seed, name, device)
         vector = is_vector(name, spec) if is_vector else len(spec.shape) == 1
         if spec.kind == "integer":

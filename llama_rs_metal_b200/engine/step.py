@@ -121,6 +121,7 @@ class _StepGraph:
         self.greedy: Optional[torch.Tensor] = None  # int32 [B]: argmax of every row, part of the graph
         self.launches = 0
         self.reports_status = False  # the graph holds kernels that write the device status word
+        self.warmed = False  # the geometry's kernels have run once outside a capture
 
     def upload(self, host: np.ndarray, keys: Optional[Sequence[int]] = None) -> None:
         i = self.turn % self.RING
@@ -463,8 +464,8 @@ class StepRunner:
 
     def _launch(self, graph: _StepGraph) -> None:
         from ..kernels import gemm_dispatch
-        if graph.graph is None:
-            self._capture(graph)
+        if graph.graph is None and not self._capture(graph):
+            return  # the step ran as plain launches; the capture waits for the geometry's next step
         graph.graph.replay()
         self.last_launches = graph.launches
         if graph.reports_status:
@@ -472,16 +473,33 @@ class StepRunner:
             # wrappers: say here that the status word has to be read at the next check
             gemm_dispatch.mark_status_dirty()
 
-    def _capture(self, graph: _StepGraph) -> None:
-        # One eager run first: it loads every kernel the step needs and writes
-        # exactly what the replay will write again, so it changes no result.
+    def _capture(self, graph: _StepGraph) -> bool:
+        """Capture the step of this geometry; True when the caller is to replay it now.
+
+        A capture records launches without running them, and kernels have to have run once
+        before they can be recorded. Where a step only writes keys and values, one plain run
+        comes first: it writes exactly what the replay writes again, so it changes no result.
+        A step that updates fixed-size state must run exactly once: there the geometry's first
+        step runs as plain launches and is the step (False), and its second step is captured."""
         def run():
             if graph.choice is None:
                 return self.model.forward(graph.ctx, self.cache)
             temperature, seed = graph.choice
             return self.model.forward_pick(graph.ctx, self.cache, temperature, seed,
                                            graph.keys if temperature is not None else None)
-        run()
+        if self.cache.state_groups and not graph.warmed:
+            graph.warmed = True
+            start = ops.launch_count()
+            if graph.choice is not None:
+                graph.ids = run()
+            else:
+                graph.logits = run()
+                graph.greedy = ops.argmax_rows(graph.logits)
+                graph.logits.greedy_ids = graph.greedy
+            self.last_launches = graph.launches = ops.launch_count() - start
+            return False
+        if not self.cache.state_groups:
+            run()
         torch.cuda.current_stream().synchronize()
         if self._pool is None:
             self._pool = torch.cuda.graph_pool_handle()
@@ -501,3 +519,4 @@ class StepRunner:
         graph.launches = ops.launch_count() - start  # the pick's two kernels included
         graph.reports_status = gemm_dispatch.status_launch_count() > status_launches
         graph.graph = captured
+        return True

@@ -179,22 +179,23 @@ class Cache:
         self.open_mask = np.zeros(max_slots, dtype=bool)      # slot is held by a sequence
         self.kv_groups: List[KeyValueGroup] = []
         self.state_groups: List[StateGroup] = []
-        # a cell is one thing one cache entry keeps: (entry,) for a plain request, (entry, i, ...)
-        # for part i of a composite one; groups and their storage are keyed by cell
-        self._where: Dict[Tuple[int, ...], Tuple[str, int]] = {}
+        # a cell is one thing one cache entry keeps: the entry's number for a plain request,
+        # (entry, i, ...) for part i of a composite one; groups and their storage are keyed by cell
+        self._where: Dict[object, Tuple[str, int]] = {}
         self._shape: Dict[int, object] = {}  # entry -> its cell, or the nested tuple of its cells
         by_request: Dict[object, List[Tuple[int, ...]]] = {}
 
         def cells_of(cell, request):
             if isinstance(request, CompositeRequest):
-                return tuple(cells_of(cell + (i,), part) for i, part in enumerate(request.parts))
+                path = (cell,) if isinstance(cell, int) else cell
+                return tuple(cells_of(path + (i,), part) for i, part in enumerate(request.parts))
             if request is None:
                 return None
             by_request.setdefault(request, []).append(cell)
             return cell
 
         for entry, request in enumerate(requests):
-            self._shape[entry] = cells_of((entry,), request)
+            self._shape[entry] = cells_of(entry, request)
         for request, entries in by_request.items():
             if isinstance(request, KeyValueRequest):
                 group = KeyValueGroup(request, entries, self.pages, max_slots, pages_per_sequence,
@@ -369,7 +370,7 @@ class Cache:
     def _view_of(self, cell):
         if cell is None:
             return None
-        if len(cell) == 0 or not isinstance(cell[0], int):
+        if not isinstance(cell, int) and (len(cell) == 0 or not isinstance(cell[0], int)):
             return tuple(self._view_of(c) for c in cell)
         kind, index = self._where.get(cell, (None, None))
         if kind == "kv":
@@ -385,7 +386,7 @@ class Cache:
         (diagnostic copy, like crates/model-runtime/src/session.rs:45-83). Positions a
         windowed group no longer keeps are NaN. A state is copied as it is. `entry` is a cache
         entry's number, or (entry, i, ...) for part i of a composite request."""
-        entry = (entry,) if isinstance(entry, int) else tuple(entry)
+        entry = entry if isinstance(entry, int) else tuple(entry)
         kind, index = self._where[entry]
         if kind != "kv":
             return self.state_groups[index].state[entry][slot].clone()

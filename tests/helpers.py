@@ -62,6 +62,80 @@ def make_model_dir(path, name, dtype=torch.bfloat16):
                               norm_mean=spec["norm_mean"], norm_std=spec["norm_std"], dtype=dtype)
 
 
+# Tiny Kikalix configurations. K1: odd sizes throughout (no size a multiple of 16, key, value and
+# query head counts all different, a layer without a feed-forward, a loop that starts after the
+# first layer and runs three times, windows shorter and longer than a page, one and three chosen
+# experts, a rotation of part of the head). K2: head size 64 on both sides of the parallel mixer,
+# so that bfloat16 runs the tensor-core products and the tiled attention kernels with the distance
+# penalty; its loop starts at the first layer. K3: a window of exactly one page, a convolution of
+# one tap (no tail), no loop, no feed-forward.
+def _moe(ff, limit, experts, top):
+    return dict(kind="moe", expert=dict(ff=ff, limit=limit), router=dict(experts=experts, top=top))
+
+
+KIKALIX = {
+    "K1": dict(
+        config=dict(architecture="Kikalix", vocab=211, width=72, norm=dict(eps=1e-6), layers=[
+            dict(type="parallel", mixer=dict(
+                left=dict(heads=4, kv_heads=2, dim=16, vdim=24, scale=0.3, mask=dict(size=7)), left_scale=0.7,
+                right=dict(heads=4, kv_heads=2, dim=24, vdim=8, conv=3, decay_rank=5, gate_rank=7), right_scale=1.3),
+                mlp=_moe(40, 1.0, 5, 3)),
+            dict(type="retention", mixer=dict(heads=3, dim=20, vdim=12, decay=[0.9, 0.97, 0.995],
+                                              rot=dict(dims=8, base=100.0)), mlp=None),
+            dict(type="parallel", mixer=dict(
+                left=dict(heads=2, kv_heads=2, dim=8, vdim=8, scale=0.5, mask=dict(size=70)), left_scale=1.0,
+                right=dict(heads=2, kv_heads=1, dim=16, vdim=16, conv=2, decay_rank=3, gate_rank=3), right_scale=0.25),
+                mlp=_moe(24, 0.5, 3, 1)),
+        ], loop=dict(start=1, stop=3, times=3)), seed=21, std=0.12),
+    "K2": dict(
+        config=dict(architecture="Kikalix", vocab=512, width=256, norm=dict(eps=1e-5), layers=[
+            dict(type="retention", mixer=dict(heads=4, dim=64, vdim=64, decay=[0.98, 0.99, 0.995, 0.999],
+                                              rot=dict(dims=64, base=10000.0)), mlp=_moe(128, 2.0, 4, 2)),
+            dict(type="parallel", mixer=dict(
+                left=dict(heads=8, kv_heads=2, dim=64, vdim=64, scale=0.125, mask=dict(size=100)), left_scale=0.5,
+                right=dict(heads=4, kv_heads=4, dim=64, vdim=64, conv=4, decay_rank=16, gate_rank=16), right_scale=0.5),
+                mlp=_moe(128, 2.0, 4, 2)),
+        ], loop=dict(start=0, stop=1, times=2)), seed=22, std=0.06),
+    "K3": dict(
+        config=dict(architecture="Kikalix", vocab=300, width=64, norm=dict(eps=1e-5), layers=[
+            dict(type="parallel", mixer=dict(
+                left=dict(heads=2, kv_heads=1, dim=32, vdim=32, scale=0.2, mask=dict(size=64)), left_scale=1.0,
+                right=dict(heads=1, kv_heads=1, dim=8, vdim=8, conv=1, decay_rank=2, gate_rank=2), right_scale=1.0),
+                mlp=None),
+            dict(type="retention", mixer=dict(heads=1, dim=16, vdim=48, decay=[0.9375], rot=dict(dims=16, base=50.0)),
+                 mlp=None),
+        ]), seed=23, std=0.15),
+}
+
+
+def make_kikalix_dir(path, name, dtype=torch.bfloat16, steady_routing=False):
+    """A model folder of a tiny Kikalix configuration with seeded random weights. Norm weights,
+    biases and the other vectors are N(0, 0.2); the routers' matrices are eight times larger than
+    the rest, so that the experts' weights differ from token to token. The choice of experts is a
+    step function of the router's input: with random weights a runner-up now and then comes
+    within a rounding of bfloat16 activations of the last chosen expert, and the engine and the
+    float64 implementation then choose differently. `steady_routing` is for comparisons in
+    bfloat16: the routers' matrices keep their size and their biases are 0, 6, 12, ..., so the same
+    experts win for every token (their weights still depend on the token) and no comparison
+    rests on a close call."""
+    from llama_rs_metal_b200.engine.model import DecoderModel
+    from llama_rs_metal_b200.registry import find_architecture
+    from llama_rs_metal_b200.runtime import Runtime
+    from llama_rs_metal_b200.weights.random_init import random_tensors, write_model_folder
+    spec = KIKALIX[name]
+    arch = find_architecture(spec["config"])
+    config = arch.config_class.from_dict(spec["config"])
+    model = DecoderModel(arch.plan(config), Runtime(torch.device("cpu"), torch.float32))
+    tensors = random_tensors(model.tensor_specs(), spec["seed"], std=spec["std"], vector_mean=0.0, vector_std=0.2,
+                             dtype=dtype)
+    for name_, t in tensors.items():
+        if name_.endswith(".router") and not steady_routing:
+            t.mul_(8.0)
+        if name_.endswith(".router.b") and steady_routing:
+            t.copy_(6.0 * torch.arange(t.numel()))
+    return write_model_folder(path, config.to_dict(), tensors, spec["seed"])
+
+
 def random_tokens(seed, length, vocab):
     rng = np.random.default_rng(seed)
     return [int(t) for t in rng.integers(0, vocab, size=length)]
@@ -179,7 +253,8 @@ def run_trace(model_dir, dtype, trace, max_tokens, out_dir, timeout=900):
         if proc.poll() is None:
             proc.kill()
     with open(os.path.join(model_dir, "config.json")) as handle:
-        vocab = json.load(handle)["vocab_size"]
+        config = json.load(handle)
+        vocab = config["vocab_size"] if "vocab_size" in config else config["vocab"]
     out = {}
     for step, rows in trace.rows.items():
         data = np.fromfile(os.path.join(out_dir, f"{step}.f32"), dtype="<f4")

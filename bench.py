@@ -202,6 +202,118 @@ def plain_cpu_point(engine):
             "tiny_a_tokens_equal": f"{same}/{len(prompts) * steps}"}
 
 
+# --------------------------------------------------------------------------- another design beside Llama
+def kikalix_shape(width, heads, kv_heads, ff, experts, top, window, layers, vocab=32768):
+    """A Kikalix configuration with layers of a real model's widths (head size 128 throughout): one
+    retention layer, then parallel layers; the first two layers loop twice."""
+    d = 128
+    moe = dict(kind="moe", expert=dict(ff=ff, limit=7.0), router=dict(experts=experts, top=top))
+    retention = dict(type="retention", mlp=moe, mixer=dict(
+        heads=heads, dim=d, vdim=d, decay=[1.0 - 2.0 ** (-5 - 3 * h / max(1, heads - 1)) for h in range(heads)],
+        rot=dict(dims=d, base=10000.0)))
+    parallel = dict(type="parallel", mlp=moe, mixer=dict(
+        left=dict(heads=heads, kv_heads=kv_heads, dim=d, vdim=d, scale=d ** -0.5, mask=dict(size=window)), left_scale=0.5,
+        right=dict(heads=heads, kv_heads=kv_heads, dim=d, vdim=d, conv=4, decay_rank=64, gate_rank=64), right_scale=0.5))
+    return dict(architecture="Kikalix", vocab=vocab, width=width, norm=dict(eps=1e-5),
+                layers=[retention] + [parallel] * (layers - 1), loop=dict(start=0, stop=2, times=2))
+
+
+DESIGN_SIZES = {   # width, heads, kv heads, expert width, experts, chosen, window, layers (two of them run twice)
+    "1k": (1024, 8, 2, 512, 8, 2, 512, 4),
+    "2k": (2048, 16, 4, 1024, 8, 2, 1024, 4),
+    "4k": (4096, 32, 8, 2048, 8, 2, 2048, 2),
+}
+
+
+def design_bench(args) -> int:
+    """Prefill and decode throughput of the Kikalix design at a few layer sizes, beside the Llama
+    decoder at equal size (the same width, head geometry, vocabulary and number of layer runs; its
+    feed-forward as wide as the experts a token uses). Random weights, one GPU, bfloat16."""
+    if args.profile:
+        os.environ["LRM_PROFILE"] = "1"
+    import numpy as np
+    import torch
+    from llama_rs_metal_b200 import Engine
+    from llama_rs_metal_b200.engine.batch import StepEntry
+    from llama_rs_metal_b200.sampling.device import DevicePick
+    peaks, peak_source = load_peaks()
+    engine = Engine(0)
+    rng = np.random.default_rng(0)
+    prompt, batch, steps = args.prefill_tokens or PREFILL_TOKENS, args.batch or 8, min(args.steps, 64)
+    sizes = [args.design_size] if args.design_size else list(DESIGN_SIZES)
+    out = {}
+
+    def measure(model, vocab, name):
+        session = model.session(context=prompt + steps + 64, max_batch=batch)
+        ids = rng.integers(0, vocab, size=prompt).tolist()
+        times = []
+        for rep in range(2 + 5):                      # prefill of one prompt: median of five after two
+            slot = session.open_slot()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            session.runner.step([StepEntry(slot, ids, (prompt - 1,))])
+            end.record()
+            torch.cuda.synchronize()
+            session.close_slot(slot)
+            if rep >= 2:
+                times.append(begin.elapsed_time(end))
+        prefill_ms = statistics.median(times)
+        slots = [session.open_slot() for _ in range(batch)]
+        for slot in slots:                            # decode: `batch` sequences of `prompt` tokens each
+            session.runner.step([StepEntry(slot, rng.integers(0, vocab, size=prompt).tolist(), ())])
+        tokens = rng.integers(0, vocab, size=(8 + steps, batch))
+        greedy = DevicePick(None, 0, [0] * batch)
+
+        def one(i):
+            if args.profile:
+                return session.runner.step_pick([StepEntry(s, [int(t)], (0,)) for s, t in zip(slots, tokens[i])], greedy)
+            return session.runner.decode_ahead(slots, tokens[i].tolist(), None, greedy)
+        for i in range(8):
+            one(i)
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for i in range(8, 8 + steps):
+            one(i)
+        end.record()
+        torch.cuda.synchronize()
+        session.runner.check_device_status()
+        decode_ms = begin.elapsed_time(end) / steps
+        for slot in slots:
+            session.close_slot(slot)
+        if args.profile:
+            from llama_rs_metal_b200.kernels import profile
+            print(f"---- {name}: every kernel alone (prompt of {prompt}, then decoding at batch {batch})", file=sys.stderr)
+            profile.report()
+            profile.reset()
+        return {"prefill_tok_s": round(prompt / (prefill_ms * 1e-3), 1), "prefill_ms": round(prefill_ms, 3),
+                "decode_tok_s": round(batch * 1000.0 / decode_ms, 1), "decode_ms_per_step": round(decode_ms, 4),
+                "weight_gb": round(model.weight_bytes / 1e9, 3)}
+
+    for size in sizes:
+        width, heads, kv_heads, ff, experts, top, window, layers = DESIGN_SIZES[size]
+        config = kikalix_shape(width, heads, kv_heads, ff, experts, top, window, layers)
+        runs = layers + 2
+        model = engine.random(config, seed=0, std=0.02, norm_mean=0.0)
+        row = {"kikalix": measure(model, config["vocab"], f"Kikalix {size}")}
+        del model
+        torch.cuda.empty_cache()
+        twin = llama(width, top * ff, runs, heads, kv_heads, 128, 8.0, False)
+        twin["vocab_size"] = config["vocab"]
+        model = engine.random(twin, seed=0, std=0.02)
+        row["llama_equal_size"] = measure(model, twin["vocab_size"], f"Llama {size}")
+        del model
+        torch.cuda.empty_cache()
+        row["shape"] = dict(width=width, heads=heads, kv_heads=kv_heads, head_dim=128, expert_ff=ff, experts=experts,
+                            top=top, window=window, layer_runs=runs)
+        out[size] = row
+    print(json.dumps({"metric": f"prefill tok/s (one {prompt}-token prompt) and decode tok/s (batch {batch} at "
+                                f"{prompt} tokens), Kikalix beside Llama at equal size",
+                      "dtype": "bf16", "data": "synthetic token ids, random-init weights", "n_gpus": 1,
+                      "decode_steps": steps, "peaks": peak_source, "cuda_graph": not args.profile, "sizes": out}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -229,8 +341,15 @@ def main() -> int:
     parser.add_argument("--profile", action="store_true",
                         help="time every kernel launch (LRM_PROFILE=1) and print the table to stderr; the "
                              "line's numbers are then those of unfused, uncaptured launches")
+    parser.add_argument("--design", choices=["kikalix"], default=None,
+                        help="instead of the default workload: prefill and decode throughput of this design at "
+                             "a few layer sizes beside the Llama decoder at equal size (see design_bench)")
+    parser.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default=None,
+                        help="with --design: one size only")
     args = parser.parse_args()
 
+    if args.design and args.impl == "ours" and args.gpus == 1:
+        return design_bench(args)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "the reference runs only through Apple's Metal API on macOS (crates/metal-backend/"

@@ -514,17 +514,18 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int):
     return ids, weights
 
 
-def moe_experts_rows(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor,
+def moe_experts_rows(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor,
                      weights: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
     """Every token's chosen experts, token by token: planes float32 [n, T, width] whose sum in plane
-    order is sum_c weights[t,c] * expert_ids[t,c](x[t]). gate, up [E, ff, width], down [E, width, ff]."""
+    order is sum_c weights[t,c] * expert_ids[t,c](x[t]). gate_up [E, 2 ff, width] (an expert's gate
+    rows, then its up rows), down [width, E, ff]."""
     _check(x, "x", dims=2)
     T, width = x.shape
-    E, ff = gate.shape[0], gate.shape[1]
-    for name, t, shape in (("gate", gate, (E, ff, width)), ("up", up, (E, ff, width)), ("down", down, (E, width, ff))):
-        _check(t, name, gate.dtype, 3)
-        if tuple(t.shape) != shape:
-            raise InvalidError(f"moe_experts_rows: {name} must be {list(shape)}")
+    _check(gate_up, "gate_up", dims=3)
+    _check(down, "down", gate_up.dtype, 3)
+    E, ff = gate_up.shape[0], gate_up.shape[1] // 2
+    if tuple(gate_up.shape) != (E, 2 * ff, width) or tuple(down.shape) != (width, E, ff):
+        raise InvalidError("moe_experts_rows: gate_up must be [E, 2 ff, width] and down [width, E, ff]")
     _check(ids, "ids", torch.int32, 2)
     _check(weights, "weights", torch.float32, 2)
     top = ids.shape[1]
@@ -535,10 +536,29 @@ def moe_experts_rows(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down
     lib = _lib()
     slices = int(lib.lrm_moe_rows_slices(T, top, ff))
     planes = _f32((top * slices, T, width), x.device)
-    _done(lib.lrm_moe_experts_rows(_ptr(x), _code(x.dtype), _ptr(gate), _ptr(up), _ptr(down), _code(gate.dtype),
-                                   _ptr(ids), _ptr(weights), _ptr(planes), T, width, ff, top, slices,
+    _done(lib.lrm_moe_experts_rows(_ptr(x), _code(x.dtype), _ptr(gate_up), _ptr(down), _code(gate_up.dtype),
+                                   _ptr(ids), _ptr(weights), _ptr(planes), T, width, ff, E, top, slices,
                                    ctypes.c_float(limit), ctypes.c_float(alpha), _stream()), "moe_experts_rows")
     return planes
+
+
+def moe_dense_gate(gate_up: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, experts: int, limit: float,
+                   alpha: float) -> torch.Tensor:
+    """From every expert's gate and up for every token, [T, E * 2 ff] (an expert's ff gate columns,
+    then its ff up columns): y [T, E * ff] = weight(t, e) * act(gate, up), zero where token t did not
+    choose expert e."""
+    _check(gate_up, "gate_up", dims=2)
+    _check(ids, "ids", torch.int32, 2)
+    _check(weights, "weights", torch.float32, 2)
+    T, top = ids.shape
+    if gate_up.shape[0] != T or gate_up.shape[1] % (2 * experts) or tuple(weights.shape) != (T, top):
+        raise InvalidError("moe_dense_gate: shapes do not agree")
+    ff = gate_up.shape[1] // (2 * experts)
+    y = _activation(T, experts * ff, gate_up.dtype, gate_up.device)
+    _done(_lib().lrm_moe_dense_gate(_ptr(gate_up), _code(gate_up.dtype), _ptr(ids), _ptr(weights), _ptr(y), T, ff,
+                                    experts, top, ctypes.c_float(limit), ctypes.c_float(alpha), _stream()),
+          "moe_dense_gate")
+    return y
 
 
 def add_row_(x: torch.Tensor, row: torch.Tensor) -> torch.Tensor:

@@ -23,11 +23,18 @@ class MixtureOfExperts(FeedForward):
     limit), y = g sigmoid(alpha g) (u + 1), output W_down y; no biases.
 
     The router's matrix is kept in float32 whatever the runtime, so its product runs on the
-    float32 kernel. The experts' matrices are stacked [experts, ...] so one launch serves every
-    choice; the choices' outputs come back as float32 planes that are added to the stream in a
-    fixed order (by the next norm where it folds them)."""
+    float32 kernel. The experts' matrices are stacked, gate_up [E, 2 ff, h] and down [h, E, ff],
+    and serve two ways of computing (csrc/moe.cu). Token by token (decoding, float32, many
+    experts per choice): one launch reads, for every token, only the experts it chose; their
+    outputs come back as float32 planes that are added to the stream in a fixed order (by the
+    next norm where it folds them). All experts at once (bfloat16 steps of DENSE_ROWS tokens and
+    more when at most DENSE_RATIO experts exist per chosen one): two tensor-core products over
+    every expert, with the weights of the experts a token did not choose set to zero between
+    them."""
 
     graph_safe = True
+    DENSE_ROWS = 64   # from this many tokens on a step is a prompt: the tensor-core products pay
+    DENSE_RATIO = 4   # experts per chosen expert up to which computing all of them is the faster way
 
     def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top: int,
                  activation: str = "clamped_gate", limit: float = 7.0, alpha: float = 1.702,
@@ -56,14 +63,22 @@ class MixtureOfExperts(FeedForward):
     def bind(self, weights, runtime) -> None:
         self.router = LinearWeight(weights["router.weight"].to(torch.float32))
         self.bias = weights["router.bias"].to(torch.float32).contiguous() if self.router_bias else None
-        stack = lambda name: torch.stack([weights[f"experts.{e}.{name}.weight"]  # noqa: E731
-                                          for e in range(self.num_experts)]).contiguous()
-        self.gate, self.up, self.down = stack("gate_proj"), stack("up_proj"), stack("down_proj")
+        E, f, h = self.num_experts, self.intermediate_size, self.hidden_size
+        self.gate_up = torch.stack([torch.cat([weights[f"experts.{e}.gate_proj.weight"],
+                                               weights[f"experts.{e}.up_proj.weight"]]) for e in range(E)]).contiguous()
+        self.down = torch.stack([weights[f"experts.{e}.down_proj.weight"] for e in range(E)], dim=1).contiguous()
+        # the same storage seen as two plain matrices, for the products over every expert
+        self.gate_up_all = LinearWeight(self.gate_up.view(E * 2 * f, h))
+        self.down_all = LinearWeight(self.down.view(h, E * f))
 
     def forward(self, x, ctx, residual):
         logits = self.router(x, out_dtype=torch.float32)
         ids, weights = ops.moe_route(logits, self.bias, self.top)
-        planes = ops.moe_experts_rows(x, self.gate, self.up, self.down, ids, weights, self.limit, self.alpha)
+        if (x.dtype == torch.bfloat16 and self.gate_up.dtype == torch.bfloat16 and x.shape[0] >= self.DENSE_ROWS
+                and self.num_experts <= self.DENSE_RATIO * self.top):
+            y = ops.moe_dense_gate(self.gate_up_all(x), ids, weights, self.num_experts, self.limit, self.alpha)
+            return self.down_all(y, epilogue=ops.ADD, out=residual, ctx=ctx)
+        planes = ops.moe_experts_rows(x, self.gate_up, self.down, ids, weights, self.limit, self.alpha)
         if ctx.may_defer:
             ctx.settle(residual)  # at most one set of partial sums is pending at a time
             ctx.pending = planes

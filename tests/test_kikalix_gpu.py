@@ -76,7 +76,8 @@ def close(got, ref, dtype, what):
     err = np.abs(got - ref).max(axis=-1) / max(float(np.abs(ref).max()), 1e-30)
     worst, beyond = int(err.argmax()), int(np.count_nonzero(err > TOLERANCE[dtype]))
     allowed = 0 if dtype == "float32" else max(1, len(err) // 20)
-    ok = beyond <= allowed and (dtype == "float32" or (err[worst] <= 0.5 and np.median(err) <= TOLERANCE[dtype] / 3))
+    ok = beyond <= allowed and (dtype == "float32" or (
+        err[worst] <= 0.5 and (len(err) < 8 or np.median(err) <= TOLERANCE[dtype] / 3)))
     assert ok, (f"{what}: {beyond} of {len(err)} rows beyond {TOLERANCE[dtype]:.0e} of the largest logit, row {worst} "
                 f"by {err[worst]:.3e}; first such row {int(np.argmax(err > TOLERANCE[dtype]))}; median {np.median(err):.3e}")
 
@@ -505,11 +506,20 @@ def test_router_and_experts_match_the_definition(dtype, T, width, ff, E, top):
     ref_logits = x.double() @ w["router"].double().T + w["router.b"].double()
     assert torch.equal(ids.cpu().long().sort(1).values, torch.topk(ref_logits, top).indices.sort(1).values)
     assert float((weights.sum(1) - 1).abs().max()) < 1e-5
-    stack = lambda n: torch.stack([w[f"e{e}.{n}"] for e in range(E)]).to(DEV).contiguous()  # noqa: E731
-    planes = ops.moe_experts_rows(x.to(DEV), stack("gate"), stack("up"), stack("down"), ids, weights, limit, alpha)
+    gate_up = torch.stack([torch.cat([w[f"e{e}.gate"], w[f"e{e}.up"]]) for e in range(E)]).to(DEV).contiguous()
+    down = torch.stack([w[f"e{e}.down"] for e in range(E)], dim=1).to(DEV).contiguous()
+    planes = ops.moe_experts_rows(x.to(DEV), gate_up, down, ids, weights, limit, alpha)
     got = ops.add_planes_(torch.zeros(T, width, device=DEV), planes).cpu().double()
     tol = 2e-5 if dtype == torch.float32 else 2e-2
     assert float((got - ref).abs().max()) <= tol * float(ref.abs().max())
+    # the same through the products over every expert, the unchosen ones' weights set to zero
+    all_gu = ops.linear(x.to(DEV), gate_up.view(E * 2 * ff, width))
+    y = ops.moe_dense_gate(all_gu, ids, weights, E, limit, alpha)
+    chosen = torch.zeros(T, E, dtype=torch.bool)
+    chosen.scatter_(1, ids.cpu().long(), True)
+    assert bool(((y.view(T, E, ff).float().abs().sum(-1) != 0).cpu() <= chosen).all())
+    got = ops.linear(y, down.view(width, E * ff), out_dtype=torch.float32).cpu().double()
+    assert float((got - ref).abs().max()) <= (2e-5 if dtype == torch.float32 else 3e-2) * float(ref.abs().max())
 
 
 # --------------------------------------------------------------------------- small pieces

@@ -63,6 +63,58 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
   for (int c = 0; c < top; ++c) w[c] /= mass;
 }
 
+// The router in one launch for steps of few tokens: one CTA per token forms the E float32 logits
+// (a warp per expert at a time, the lanes across the row, each lane's products in ascending order
+// and the lanes added by a butterfly: a fixed order whatever the batch), then thread 0 chooses.
+template <typename A>
+__global__ void moe_router_kernel(const A* __restrict__ x, const float* __restrict__ w,
+                                  const float* __restrict__ bias, int* __restrict__ ids,
+                                  float* __restrict__ weights, float* __restrict__ logits, int width, int E,
+                                  int top) {
+  extern __shared__ float smem[];
+  float* xs = smem;          // [width]
+  float* zs = smem + width;  // [E]
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f32(x[static_cast<size_t>(t) * width + i]);
+  __syncthreads();
+  for (int e = warp; e < E; e += warps) {
+    const float* row = w + static_cast<size_t>(e) * width;
+    float acc = 0.f;
+    for (int i = lane; i < width; i += 32) acc = fmaf(row[i], xs[i], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) zs[e] = acc + (bias != nullptr ? bias[e] : 0.f);
+  }
+  __syncthreads();
+  if (logits != nullptr)
+    for (int e = threadIdx.x; e < E; e += blockDim.x) logits[static_cast<size_t>(t) * E + e] = zs[e];
+  if (threadIdx.x != 0) return;
+  int* mine = ids + static_cast<size_t>(t) * top;
+  float* out = weights + static_cast<size_t>(t) * top;
+  float best = -INFINITY, mass = 0.f;
+  for (int c = 0; c < top; ++c) {
+    int arg = -1;
+    float val = -INFINITY;
+    for (int e = 0; e < E; ++e) {
+      bool taken = false;
+      for (int p = 0; p < c; ++p) taken |= mine[p] == e;
+      if (!taken && (arg < 0 || zs[e] > val)) {
+        arg = e;
+        val = zs[e];
+      }
+    }
+    mine[c] = arg;
+    out[c] = val;
+    if (c == 0) best = val;
+  }
+  for (int c = 0; c < top; ++c) {
+    out[c] = expf(out[c] - best);
+    mass += out[c];
+  }
+  for (int c = 0; c < top; ++c) out[c] /= mass;
+}
+
 template <typename T> struct Pack8;
 template <> struct Pack8<__nv_bfloat16> {
   static constexpr int N = 8;
@@ -104,6 +156,52 @@ __device__ __forceinline__ float row_dot(const W* __restrict__ w, const float* _
   return warp_sum(acc);
 }
 
+// two rows against the same vector, their loads issued together (twice the bytes in flight)
+template <typename W>
+__device__ __forceinline__ void row_dot2(const W* __restrict__ a, const W* __restrict__ b,
+                                         const float* __restrict__ x, int n, bool vector_ok, int lane,
+                                         float* ra, float* rb) {
+  constexpr int N = Pack8<W>::N;
+  float acc_a = 0.f, acc_b = 0.f;
+  if (vector_ok) {
+    int i = lane * N;
+    for (; i + 32 * N < n; i += 64 * N) {  // two chunks of each row per trip
+      float fa[N], fb[N], ga[N], gb[N];
+      Pack8<W>::load(a + i, fa);
+      Pack8<W>::load(b + i, fb);
+      Pack8<W>::load(a + i + 32 * N, ga);
+      Pack8<W>::load(b + i + 32 * N, gb);
+#pragma unroll
+      for (int e = 0; e < N; ++e) {
+        acc_a = fmaf(fa[e], x[i + e], acc_a);
+        acc_b = fmaf(fb[e], x[i + e], acc_b);
+      }
+#pragma unroll
+      for (int e = 0; e < N; ++e) {
+        acc_a = fmaf(ga[e], x[i + 32 * N + e], acc_a);
+        acc_b = fmaf(gb[e], x[i + 32 * N + e], acc_b);
+      }
+    }
+    for (; i < n; i += 32 * N) {
+      float fa[N], fb[N];
+      Pack8<W>::load(a + i, fa);
+      Pack8<W>::load(b + i, fb);
+#pragma unroll
+      for (int e = 0; e < N; ++e) {
+        acc_a = fmaf(fa[e], x[i + e], acc_a);
+        acc_b = fmaf(fb[e], x[i + e], acc_b);
+      }
+    }
+  } else {
+    for (int i = lane; i < n; i += 32) {
+      acc_a = fmaf(to_f32(a[i]), x[i], acc_a);
+      acc_b = fmaf(to_f32(b[i]), x[i], acc_b);
+    }
+  }
+  *ra = warp_sum(acc_a);
+  *rb = warp_sum(acc_b);
+}
+
 template <typename A, typename W>
 __global__ __launch_bounds__(256) void moe_experts_rows_kernel(
     const A* __restrict__ x, const W* __restrict__ gate_up, const W* __restrict__ down,
@@ -125,8 +223,8 @@ __global__ __launch_bounds__(256) void moe_experts_rows_kernel(
   const W* wd = down + static_cast<size_t>(e) * ff;  // row r of this expert: wd + r * experts * ff
   const bool wide_ok = width % Pack8<W>::N == 0;
   for (int f = f0 + warp; f < f1; f += warps) {
-    float g = row_dot(wg + static_cast<size_t>(f) * width, xs, width, wide_ok, lane);
-    float u = row_dot(wu + static_cast<size_t>(f) * width, xs, width, wide_ok, lane);
+    float g, u;
+    row_dot2(wg + static_cast<size_t>(f) * width, wu + static_cast<size_t>(f) * width, xs, width, wide_ok, lane, &g, &u);
     if (lane == 0) {
       g = fminf(g, limit);
       u = fminf(fmaxf(u, -limit), limit);
@@ -209,12 +307,33 @@ LRM_API int lrm_moe_route(const float* logits, const float* bias, int* ids, floa
   return 0;
 }
 
+// x [T, width] float32 or bfloat16 (widened to float32), w float32 [E, width], bias float32 [E] or
+// null -> ids int32 [T, top], weights float32 [T, top]; `logits` (float32 [T, E]) may be null.
+LRM_API int lrm_moe_router(const void* x, int x_dtype, const float* w, const float* bias, int* ids,
+                           float* weights, float* logits, int tokens, int width, int E, int top,
+                           cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (width <= 0 || E <= 0 || top <= 0 || top > E) return LRM_BAD_ARGUMENT;
+  const size_t bytes = sizeof(float) * (static_cast<size_t>(width) + E);
+  if (bytes > 48 * 1024) return LRM_UNSUPPORTED;
+  const int threads = E >= 8 ? 256 : 128;
+  if (x_dtype == LRM_F32)
+    LRM_LAUNCH(moe_router_kernel<float>, tokens, threads, bytes, stream, static_cast<const float*>(x), w, bias, ids,
+               weights, logits, width, E, top);
+  else if (x_dtype == LRM_BF16)
+    LRM_LAUNCH(moe_router_kernel<__nv_bfloat16>, tokens, threads, bytes, stream,
+               static_cast<const __nv_bfloat16*>(x), w, bias, ids, weights, logits, width, E, top);
+  else
+    return LRM_BAD_ARGUMENT;
+  return 0;
+}
+
 // How many slices of the inner width a step of `tokens` tokens is cut into: enough CTAs to fill
-// the device, no slice shorter than 64.
+// the device, no slice shorter than 32.
 LRM_API int lrm_moe_rows_slices(int tokens, int top, int ff) {
   const long long items = static_cast<long long>(tokens) * top;
-  long long want = (2 * 148 + items - 1) / items;
-  const int most = ff / 64 > 0 ? ff / 64 : 1;
+  long long want = (4 * 148 + items - 1) / items;
+  const int most = ff / 32 > 0 ? ff / 32 : 1;
   if (want > most) want = most;
   return want < 1 ? 1 : static_cast<int>(want);
 }

@@ -11,12 +11,13 @@
 //
 // The scan: one CTA per (sequence, head, tile of value columns). Columns of S do not depend on
 // one another, so a CTA keeps its columns in registers for the whole step: thread (column j,
-// part p of P) holds rows p, p + P, p + 2P, ... of column j. Per token every thread forms, over its
+// part p of P) holds a run of consecutive rows of column j. Per token every thread forms, over its
 // rows, the three partial sums  r = sum g_i S_ij k_i,  s = sum g_i S_ij q_i,  c = sum k_i q_i,
 // which are added over the P parts by shuffles, and then
 //   u_j = b (v_j - r)   (or v_j without the delta rule),   o_j = s + u_j c,   S_ij <- g_i S_ij + k_i u_j,
 // which is the update above with the read-out taken after the write. Tokens are staged through
-// shared memory a chunk at a time, so the inner loop has no block-wide barrier. A step of one
+// shared memory a chunk at a time by asynchronous copies, the next chunk under way while this
+// one is worked on, so the inner loop has no block-wide barrier and waits for no load. A step of one
 // token (decoding) and a step of a whole prompt run the same arithmetic in the same order, so
 // the state after a prompt does not depend on how it was cut.
 //
@@ -28,19 +29,29 @@ namespace {
 constexpr int kScanThreads = 128;
 constexpr int kChunk = 16;
 
+__device__ __forceinline__ void scan_cp_async(float* dst, const float* src, bool valid, bool wide) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+  if (wide)
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(valid ? 16 : 0));
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(d), "l"(src), "r"(valid ? 4 : 0));
+}
+
+// Thread (column j, part p) holds rows p * ROWS .. p * ROWS + ROWS - 1 of column j. A token's q, k
+// and g rows lie in shared memory as [P][ROWS + 4] (the 4 floats between the parts keep the parts'
+// 16-byte reads on different banks); tokens come in chunks of kChunk, two chunks in flight.
 template <int ROWS, bool DELTA>
 __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
     const float* __restrict__ g, const float* __restrict__ head_decay, const float* __restrict__ beta,
     float* __restrict__ state, float* __restrict__ out, const int* __restrict__ cu_seqlens,
     const int* __restrict__ slots, int H, int KH, int d, int dv, int P) {
-  extern __shared__ float smem[];
-  const int DP = ROWS * P, COLS = kScanThreads / P;
-  float* qs = smem;                    // [kChunk][DP]
-  float* ks = qs + kChunk * DP;        // [kChunk][DP]
-  float* gs = ks + kChunk * DP;        // [kChunk][DP] (delta rule only)
-  float* vs = gs + (DELTA ? kChunk * DP : 0);  // [kChunk][COLS]
-  float* bs = vs + kChunk * COLS;      // [kChunk]
+  extern __shared__ __align__(16) float smem[];
+  constexpr int RS = ROWS + 4;
+  const int TS = P * RS, COLS = kScanThreads / P;
+  const int VS = (COLS + 3) & ~3;                       // v of a token, padded to whole 16 bytes
+  const int TOKEN = (DELTA ? 3 : 2) * TS + VS + 4;      // q | k | (g) | v | beta
+  const int STAGE = kChunk * TOKEN;
 
   const int tid = threadIdx.x, pidx = tid % P, jl = tid / P;
   const int h = blockIdx.y, b = blockIdx.z, kh = h / (H / KH);
@@ -52,61 +63,93 @@ __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
   float* mine = slot >= 0 ? state + (static_cast<size_t>(slot) * H + h) * d * dv : nullptr;
 #pragma unroll
   for (int i = 0; i < ROWS; ++i) {
-    const int row = i * P + pidx;
+    const int row = pidx * ROWS + i;
     S[i] = (mine != nullptr && row < d && j < dv) ? mine[static_cast<size_t>(row) * dv + j] : 0.f;
   }
   const float a = DELTA ? 1.f : head_decay[h];
+  // 16-byte copies where every row of the inputs starts on a 16-byte boundary
+  const bool wide = d % 4 == 0 && dv % 4 == 0 && COLS % 4 == 0;
+  const int step = wide ? 4 : 1;
 
-  for (int c0 = 0; c0 < n; c0 += kChunk) {
+  auto issue = [&](int c0, int stage) {
+    float* base = smem + stage * STAGE;
     const int cn = min(kChunk, n - c0);
-    __syncthreads();
-    for (int idx = tid; idx < cn * DP; idx += kScanThreads) {
-      const int c = idx / DP, r = idx % DP;
+    const int per_token = ROWS * P / step;  // granules of a q (k, g) row, padding rows included
+    for (int idx = tid; idx < cn * per_token; idx += kScanThreads) {
+      const int c = idx / per_token, r = (idx % per_token) * step;
       const size_t tok = static_cast<size_t>(start + c0 + c);
       const bool in = r < d;
-      qs[idx] = in ? q[(tok * KH + kh) * d + r] : 0.f;
-      ks[idx] = in ? k[(tok * KH + kh) * d + r] : 0.f;
-      if (DELTA) gs[idx] = in ? g[(tok * H + h) * d + r] : 1.f;
+      float* dst = base + c * TOKEN + (r / ROWS) * RS + r % ROWS;
+      scan_cp_async(dst, q + (tok * KH + kh) * d + (in ? r : 0), in, wide);
+      scan_cp_async(dst + TS, k + (tok * KH + kh) * d + (in ? r : 0), in, wide);
+      if (DELTA) scan_cp_async(dst + 2 * TS, g + (tok * H + h) * d + (in ? r : 0), in, wide);
     }
-    for (int idx = tid; idx < cn * COLS; idx += kScanThreads) {
-      const int c = idx / COLS, col = blockIdx.x * COLS + idx % COLS;
+    const int v_per_token = COLS / step;
+    for (int idx = tid; idx < cn * v_per_token; idx += kScanThreads) {
+      const int c = idx / v_per_token, cl = (idx % v_per_token) * step, col = blockIdx.x * COLS + cl;
       const size_t tok = static_cast<size_t>(start + c0 + c);
-      vs[idx] = col < dv ? v[(tok * H + h) * dv + col] : 0.f;
+      const bool in = col < dv;
+      scan_cp_async(base + c * TOKEN + (DELTA ? 3 : 2) * TS + cl, v + (tok * H + h) * dv + (in ? col : 0), in, wide);
     }
     if (DELTA)
-      for (int c = tid; c < cn; c += kScanThreads) bs[c] = beta[static_cast<size_t>(start + c0 + c) * H + h];
+      for (int c = tid; c < cn; c += kScanThreads)
+        scan_cp_async(base + c * TOKEN + 3 * TS + VS, beta + static_cast<size_t>(start + c0 + c) * H + h, true, false);
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+
+  if (n > 0) issue(0, 0);
+  for (int c0 = 0, it = 0; c0 < n; c0 += kChunk, ++it) {
+    const int cn = min(kChunk, n - c0);
+    if (c0 + kChunk < n) {
+      issue(c0 + kChunk, (it + 1) & 1);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
+    }
     __syncthreads();
+    const float* base = smem + (it & 1) * STAGE;
     for (int c = 0; c < cn; ++c) {
-      const float* qc = qs + c * DP + pidx;
-      const float* kc = ks + c * DP + pidx;
-      const float* gc = gs + c * DP + pidx;
-      float r = 0.f, s = 0.f, kq = 0.f;
+      const float* qc = base + c * TOKEN + pidx * RS;
+      const float* kc = qc + TS;
+      const float* gc = kc + TS;
+      float kr[ROWS];
+      float r0 = 0.f, r1 = 0.f, s0 = 0.f, s1 = 0.f, kq0 = 0.f, kq1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < ROWS; ++i) {
-        const float ki = kc[i * P], qi = qc[i * P];
-        const float sg = S[i] * (DELTA ? gc[i * P] : a);
-        S[i] = sg;
-        if (DELTA) r = fmaf(sg, ki, r);
-        s = fmaf(sg, qi, s);
-        kq = fmaf(ki, qi, kq);
+      for (int i = 0; i < ROWS; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kc + i);
+        const float4 q4 = *reinterpret_cast<const float4*>(qc + i);
+        float4 g4 = make_float4(a, a, a, a);
+        if (DELTA) g4 = *reinterpret_cast<const float4*>(gc + i);
+        kr[i] = k4.x, kr[i + 1] = k4.y, kr[i + 2] = k4.z, kr[i + 3] = k4.w;
+        S[i] *= g4.x, S[i + 1] *= g4.y, S[i + 2] *= g4.z, S[i + 3] *= g4.w;
+        if (DELTA) {
+          r0 = fmaf(S[i], k4.x, r0), r1 = fmaf(S[i + 1], k4.y, r1);
+          r0 = fmaf(S[i + 2], k4.z, r0), r1 = fmaf(S[i + 3], k4.w, r1);
+        }
+        s0 = fmaf(S[i], q4.x, s0), s1 = fmaf(S[i + 1], q4.y, s1);
+        s0 = fmaf(S[i + 2], q4.z, s0), s1 = fmaf(S[i + 3], q4.w, s1);
+        kq0 = fmaf(k4.x, q4.x, kq0), kq1 = fmaf(k4.y, q4.y, kq1);
+        kq0 = fmaf(k4.z, q4.z, kq0), kq1 = fmaf(k4.w, q4.w, kq1);
       }
+      float r = r0 + r1, s = s0 + s1, kq = kq0 + kq1;
       for (int o = 1; o < P; o <<= 1) {
         if (DELTA) r += __shfl_xor_sync(0xffffffffu, r, o);
         s += __shfl_xor_sync(0xffffffffu, s, o);
         kq += __shfl_xor_sync(0xffffffffu, kq, o);
       }
-      const float vj = vs[c * COLS + jl];
-      const float u = DELTA ? bs[c] * (vj - r) : vj;
+      const float vj = base[c * TOKEN + (DELTA ? 3 : 2) * TS + jl];
+      const float u = DELTA ? base[c * TOKEN + 3 * TS + VS] * (vj - r) : vj;
 #pragma unroll
-      for (int i = 0; i < ROWS; ++i) S[i] = fmaf(kc[i * P], u, S[i]);
+      for (int i = 0; i < ROWS; ++i) S[i] = fmaf(kr[i], u, S[i]);
       if (pidx == 0 && j < dv)
         out[(static_cast<size_t>(start + c0 + c) * H + h) * dv + j] = fmaf(u, kq, s);
     }
+    __syncthreads();
   }
   if (mine != nullptr) {
 #pragma unroll
     for (int i = 0; i < ROWS; ++i) {
-      const int row = i * P + pidx;
+      const int row = pidx * ROWS + i;
       if (row < d && j < dv) mine[static_cast<size_t>(row) * dv + j] = S[i];
     }
   }
@@ -116,8 +159,8 @@ template <int ROWS, bool DELTA>
 int launch_scan(const float* q, const float* k, const float* v, const float* g, const float* head_decay,
                 const float* beta, float* state, float* out, const int* cu_seqlens, const int* slots,
                 int seqs, int H, int KH, int d, int dv, int P, cudaStream_t stream) {
-  const int DP = ROWS * P, COLS = kScanThreads / P;
-  const size_t bytes = sizeof(float) * (static_cast<size_t>(kChunk) * DP * (DELTA ? 3 : 2) + kChunk * COLS + kChunk);
+  const int COLS = kScanThreads / P, TS = P * (ROWS + 4), VS = (COLS + 3) & ~3;
+  const size_t bytes = sizeof(float) * 2 * kChunk * (static_cast<size_t>(DELTA ? 3 : 2) * TS + VS + 4);
   static bool raised = false;  // per instantiation
   if (bytes > 48 * 1024 && !raised) {
     cudaError_t e = cudaFuncSetAttribute(linear_scan_kernel<ROWS, DELTA>,

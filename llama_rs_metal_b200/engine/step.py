@@ -68,6 +68,7 @@ def _tell_profiler(before: Sequence[int], counts: Sequence[int], phase: str = ""
     from ..kernels import profile
     if profile.enabled:
         profile.hints["phase"] = phase
+        profile.hints["tokens"] = float(sum(counts))
         profile.hints["kv_tokens"] = float(sum(b + n for b, n in zip(before, counts)))
         profile.hints["pairs"] = float(sum(n * b + n * (n + 1) // 2 for b, n in zip(before, counts)))
 

@@ -514,6 +514,27 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int):
     return ids, weights
 
 
+def moe_router(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], top: int):
+    """moe_route(x . weight^T, bias, top) in one launch: float32 logits from x [T, width] (float32, or
+    bfloat16 widened exactly) and float32 weight [E, width], a CTA per token. For steps of few
+    tokens; None where the kernel does not take the sizes (the caller makes the product and routes)."""
+    _check(x, "x", dims=2)
+    _check(weight, "weight", torch.float32, 2)
+    T, width = x.shape
+    E = weight.shape[0]
+    if weight.shape[1] != width or not 0 < top <= E:
+        raise InvalidError("moe_router: shapes do not agree")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+    if 4 * (width + E) > 48 * 1024:
+        return None
+    ids = torch.empty((T, top), dtype=torch.int32, device=x.device)
+    weights = _f32((T, top), x.device)
+    _done(_lib().lrm_moe_router(_ptr(x), _code(x.dtype), _ptr(weight), _ptr(bias), _ptr(ids), _ptr(weights), None,
+                                T, width, E, top, _stream()), "moe_router")
+    return ids, weights
+
+
 def moe_experts_rows(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor,
                      weights: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
     """Every token's chosen experts, token by token: planes float32 [n, T, width] whose sum in plane

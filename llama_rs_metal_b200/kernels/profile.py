@@ -30,7 +30,7 @@ enabled = os.environ.get("LRM_PROFILE", "0") == "1"
 
 # what the host knows about the step that is running and the kernels cannot tell from their
 # arguments: tokens whose keys attention reads, and query-key pairs of a prompt's causal attention
-hints: Dict[str, float] = {"kv_tokens": 0, "pairs": 0, "phase": ""}
+hints: Dict[str, float] = {"kv_tokens": 0, "pairs": 0, "phase": "", "tokens": 0}
 
 _ELEM = {0: 4, 1: 2}  # dtype codes of the C entry points -> bytes per element
 
@@ -79,6 +79,30 @@ WORK: Dict[str, Callable[..., Tuple[float, float]]] = {
     "lrm_attention_extend_tiled": lambda a: (2.0 * hints["kv_tokens"] * _v(a[12]) * _v(a[13]) * 2,
                                              4.0 * hints["pairs"] * _v(a[11]) * _v(a[13])),
     "lrm_argmax_rows": lambda a: (4.0 * _v(a[4]) * _v(a[5]), 0),
+    # the state scan: every sequence's state read and written once, the step's float32 inputs and outputs
+    # once; per token and state element a decay, two (three with the delta rule) sums and the update
+    "lrm_linear_state_scan": lambda a: (
+        8.0 * _v(a[10]) * _v(a[11]) * _v(a[13]) * _v(a[14])
+        + 4.0 * hints["tokens"] * (2 * _v(a[12]) * _v(a[13]) + 2 * _v(a[11]) * _v(a[14])
+                                   + (_v(a[11]) * (_v(a[13]) + 1) if a[3].value else 0)),
+        hints["tokens"] * _v(a[11]) * _v(a[13]) * _v(a[14]) * (7.0 if a[3].value else 5.0)),
+    "lrm_retention_prepare": lambda a: (_v(a[13]) * _v(a[14]) * (2 * _v(a[15]) + _v(a[16])) * (_ELEM[_v(a[1])] + 4.0), 0),
+    "lrm_delta_prepare": lambda a: (
+        _v(a[20]) * ((2 * _v(a[23]) * _v(a[24]) + _v(a[22]) * _v(a[25])) * (_ELEM[_v(a[1])] + 4.0)
+                     + _v(a[22]) * (_v(a[24]) * 8.0 + 4.0)), 0),
+    "lrm_head_norm_gate": lambda a: (_v(a[8]) * _v(a[9]) * _v(a[10]) * (4.0 + _ELEM[_v(a[3])] + _ELEM[_v(a[7])]), 0),
+    "lrm_qkv_bias_store": lambda a: (2.0 * _v(a[9]) * (_v(a[10]) * _v(a[12]) + _v(a[11]) * (_v(a[12]) + _v(a[13])))
+                                     * _ELEM[_v(a[1])], 0),
+    # token by token: an expert's three matrices once per (token, choice) that reads them, at most once
+    # per expert from memory; the planes written
+    "lrm_moe_experts_rows": lambda a: (
+        min(_v(a[8]) * _v(a[12]), _v(a[11])) * 3.0 * _v(a[10]) * _v(a[9]) * _ELEM[_v(a[4])]
+        + 4.0 * _v(a[8]) * _v(a[12]) * _v(a[13]) * _v(a[9]),
+        6.0 * _v(a[8]) * _v(a[12]) * _v(a[10]) * _v(a[9])),
+    "lrm_moe_dense_gate": lambda a: (3.0 * _v(a[5]) * _v(a[6]) * _v(a[7]) * _ELEM[_v(a[1])], 0),
+    "lrm_moe_router": lambda a: (_v(a[7]) * _v(a[8]) * _ELEM[_v(a[1])] + 4.0 * _v(a[9]) * _v(a[8]), 2.0 * _v(a[7]) * _v(a[8]) * _v(a[9])),
+    "lrm_moe_route": lambda a: (_v(a[4]) * (_v(a[5]) * 4.0 + _v(a[6]) * 8.0), 0),
+    "lrm_add_row": lambda a: (8.0 * _v(a[2]) * _v(a[3]), 0),
     "lrm_sample_gumbel_rows": lambda a: (4.0 * _v(a[4]) * _v(a[5]), 0),
 }
 # entry points that only answer questions and launch nothing

@@ -33,6 +33,7 @@ class MixtureOfExperts(FeedForward):
     them."""
 
     graph_safe = True
+    ROUTER_ROWS = 256  # up to this many tokens the router always runs as one launch, a CTA per token
     DENSE_ROWS = 64   # from this many tokens on a step is a prompt: the tensor-core products pay
     DENSE_RATIO = 4   # experts per chosen expert up to which computing all of them is the faster way
 
@@ -71,9 +72,18 @@ class MixtureOfExperts(FeedForward):
         self.gate_up_all = LinearWeight(self.gate_up.view(E * 2 * f, h))
         self.down_all = LinearWeight(self.down.view(h, E * f))
 
+    def route(self, x):
+        """(expert ids int32 [T, top], weights float32 [T, top]). One launch per step; steps of
+        many tokens make the logits with the float32 matrix kernel first when there are many
+        experts to a token's CTA."""
+        routed = ops.moe_router(x, self.router.weight, self.bias, self.top) \
+            if x.shape[0] <= self.ROUTER_ROWS or self.num_experts <= 16 else None
+        if routed is None:
+            routed = ops.moe_route(self.router(x, out_dtype=torch.float32), self.bias, self.top)
+        return routed
+
     def forward(self, x, ctx, residual):
-        logits = self.router(x, out_dtype=torch.float32)
-        ids, weights = ops.moe_route(logits, self.bias, self.top)
+        ids, weights = self.route(x)
         if (x.dtype == torch.bfloat16 and self.gate_up.dtype == torch.bfloat16 and x.shape[0] >= self.DENSE_ROWS
                 and self.num_experts <= self.DENSE_RATIO * self.top):
             y = ops.moe_dense_gate(self.gate_up_all(x), ids, weights, self.num_experts, self.limit, self.alpha)

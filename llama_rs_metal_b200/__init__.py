@@ -1,4 +1,5 @@
-"""A small B200-native inference library for the Llama 3 dense decoder.
+"""A small B200-native inference library for decoders put together from registered parts: the
+Llama 3 dense decoder and the Kikalix decoder (state mixers, windowed attention, experts).
 
 Public surface (after crates/llama-rs/src/lib.rs): Engine, Model, Session,
 GenerationOptions, Sampling, GenerationResult, and the typed errors.

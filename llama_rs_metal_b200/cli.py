@@ -46,7 +46,7 @@ def _sample_args(parser: argparse.ArgumentParser) -> None:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    parser = argparse.ArgumentParser(prog="llama-cli", description="B200 inference for the Llama 3 dense decoder")
+    parser = argparse.ArgumentParser(prog="llama-cli", description="B200 inference for the registered decoders (Llama 3 dense, Kikalix)")
     commands = parser.add_subparsers(dest="command", required=True)
     inspect = commands.add_parser("inspect", help="Inspect a model folder without initializing the GPU")
     inspect.add_argument("model")
@@ -63,7 +63,9 @@ def build_parser() -> argparse.ArgumentParser:
     random.add_argument("--out", required=True)
     random.add_argument("--seed", type=int, default=0)
     random.add_argument("--std", type=float, default=0.02)
-    random.add_argument("--norm-std", type=float, default=0.0, help="norm weights are N(1, this)")
+    random.add_argument("--norm-mean", type=float, default=1.0,
+                        help="mean of norm weights and other vectors (0 for an architecture whose norms add 1)")
+    random.add_argument("--norm-std", type=float, default=0.0, help="norm weights are N(norm-mean, this)")
     random.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     return parser
 
@@ -117,7 +119,8 @@ def run_random(args) -> int:
     with open(args.config, "r", encoding="utf-8") as handle:
         config = json.load(handle)
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
-    path = write_random_model(args.out, config, seed=args.seed, std=args.std, norm_std=args.norm_std, dtype=dtype)
+    path = write_random_model(args.out, config, seed=args.seed, std=args.std, norm_mean=args.norm_mean,
+                              norm_std=args.norm_std, dtype=dtype)
     print(path)
     return 0
 

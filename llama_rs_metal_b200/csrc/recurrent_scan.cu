@@ -108,6 +108,7 @@ __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
     }
     __syncthreads();
     const float* base = smem + (it & 1) * STAGE;
+#pragma unroll 2
     for (int c = 0; c < cn; ++c) {
       const float* qc = base + c * TOKEN + pidx * RS;
       const float* kc = qc + TS;
@@ -177,9 +178,11 @@ int launch_scan(const float* q, const float* k, const float* v, const float* g, 
 // How a head's key rows are cut over threads: P parts (a power of two up to 32) of ROWS rows.
 // Few parts when the head is small (less to add up by shuffles), more when it is large (the
 // registers a thread can keep bound ROWS to 64).
+int g_scan_rows = 16;  // most rows a thread holds (tuning: lrm_linear_state_scan_rows)
+
 void scan_shape(int d, int* rows, int* parts) {
   int P = 1;
-  while (P < 32 && (d + P - 1) / P > 16) P <<= 1;
+  while (P < 32 && (d + P - 1) / P > g_scan_rows) P <<= 1;
   int need = (d + P - 1) / P, R = 4;
   while (R < need) R <<= 1;
   *rows = R;
@@ -381,6 +384,13 @@ __global__ void conv_tail_update_kernel(const A* __restrict__ proj, long long st
 }
 
 }  // namespace
+
+// Tuning: the most rows of a state column one thread holds (4, 8, 16, 32 or 64; more rows mean fewer
+// parts to add up by shuffles and longer chains of sums per thread). Returns the value in force.
+LRM_API int lrm_linear_state_scan_rows(int rows) {
+  if (rows == 4 || rows == 8 || rows == 16 || rows == 32 || rows == 64) g_scan_rows = rows;
+  return g_scan_rows;
+}
 
 // q, k float32 [T, KH, d]; v float32 [T, H, dv]; out float32 [T, H, dv]; state float32
 // [slots, H, d, dv]. Without `g`: plain decay per head (head_decay [H]); with it: the gated delta

@@ -1,6 +1,6 @@
 """The Kikalix decoder as a plan of parts.
 
-Layers are pre-norm (norm weights stored around zero): a mixer, then a mixture of experts or
+Layers are pre-norm (a norm multiplies by 1 + its stored weight): a mixer, then a mixture of experts or
 nothing. Two kinds of mixer: `retention` (a decayed outer-product state with rotary positions),
 and `parallel`, a weighted sum of windowed grouped-query attention with a linear distance
 penalty (biases on q, k, v, no rotation) and a gated delta rule. A run of layers may loop: it

@@ -15,7 +15,7 @@ from .base import Norm
 class RMSNorm(Norm):
     """y = x / sqrt(mean(x^2) + eps) * (offset + w), statistics in float32
     (crates/metal-backend/src/shaders/elementwise.metal:31-46; no +1 offset for Llama).
-    `offset` 1 is for weights stored around zero; the sum is made once, in float32, when the
+    `offset` 1 is for checkpoints that keep a norm's weight as its difference from 1; the sum is made once, in float32, when the
     weights are bound."""
 
     graph_safe = True

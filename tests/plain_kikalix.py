@@ -43,7 +43,7 @@ def unit_rms(x, eps):
 
 
 def offset_norm(x, w, eps):
-    """RMS norm whose weight is stored around zero."""
+    """RMS norm that multiplies by 1 + w."""
     return unit_rms(x, eps) * (1.0 + w)
 
 

@@ -122,7 +122,7 @@ def make_kikalix_dir(path, name, dtype=torch.bfloat16, steady_routing=False):
     from llama_rs_metal_b200.registry import find_architecture
     from llama_rs_metal_b200.runtime import Runtime
     from llama_rs_metal_b200.weights.random_init import random_tensors, write_model_folder
-    spec = KIKALIX[name]
+    spec = KIKALIX[name] if isinstance(name, str) else name   # or a spec of the caller's own
     arch = find_architecture(spec["config"])
     config = arch.config_class.from_dict(spec["config"])
     model = DecoderModel(arch.plan(config), Runtime(torch.device("cpu"), torch.float32))

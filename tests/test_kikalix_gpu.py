@@ -70,14 +70,17 @@ def reference(plain, name, tokens, dtype="float32"):
 TOLERANCE = {"float32": 1e-4, "bfloat16": 6e-2}
 
 
-def close(got, ref, dtype, what):
+def close(got, ref, dtype, what, drawn=False):
+    """`drawn`: a configuration drawn at random may have heads of four values or a window of one
+    key, where bfloat16 rounding weighs more than in the fixed configurations; there bfloat16 is
+    only held to being finite, near in the median and nowhere far off (float32 stays strict)."""
     got, ref = np.asarray(got, dtype=np.float64), np.asarray(ref, dtype=np.float64)
     assert got.shape == ref.shape and np.all(np.isfinite(got)), what
     err = np.abs(got - ref).max(axis=-1) / max(float(np.abs(ref).max()), 1e-30)
     worst, beyond = int(err.argmax()), int(np.count_nonzero(err > TOLERANCE[dtype]))
-    allowed = 0 if dtype == "float32" else max(1, len(err) // 20)
+    allowed = 0 if dtype == "float32" else len(err) if drawn else max(1, len(err) // 20)
     ok = beyond <= allowed and (dtype == "float32" or (
-        err[worst] <= 0.5 and (len(err) < 8 or np.median(err) <= TOLERANCE[dtype] / 3)))
+        err[worst] <= 0.5 and (len(err) < 8 or np.median(err) <= TOLERANCE[dtype] / (1 if drawn else 3))))
     assert ok, (f"{what}: {beyond} of {len(err)} rows beyond {TOLERANCE[dtype]:.0e} of the largest logit, row {worst} "
                 f"by {err[worst]:.3e}; first such row {int(np.argmax(err > TOLERANCE[dtype]))}; median {np.median(err):.3e}")
 
@@ -538,3 +541,70 @@ def test_norm_with_an_offset_and_row_added_to_the_stream():
     y = x.clone()
     ops.add_row_(y, row)
     assert torch.equal(y, x + row)
+
+
+# --------------------------------------------------------------------------- configurations drawn at random
+def drawn_configuration(seed):
+    """Sizes, head counts, layer order, windows, constants and the loop, all drawn: nothing in the
+    library may rest on the values of one model."""
+    rng = np.random.default_rng(seed)
+    pick = lambda *values: values[int(rng.integers(len(values)))]  # noqa: E731
+    width = int(pick(40, 64, 100, 136))
+    layers = []
+    for _ in range(int(rng.integers(2, 5))):
+        experts = int(pick(2, 3, 6, 9))
+        mlp = None if rng.random() < 0.25 else helpers._moe(int(pick(8, 20, 32, 56)), float(pick(0.5, 1.5, 7.0)), experts,
+                                                            int(rng.integers(1, experts + 1)))
+        if rng.random() < 0.4:
+            heads, dim = int(pick(1, 2, 5)), int(pick(6, 16, 32))
+            dims = int(pick(2, dim // 2 * 2, dim // 2 // 2 * 2 or 2))
+            layers.append(dict(type="retention", mlp=mlp, mixer=dict(
+                heads=heads, dim=dim, vdim=int(pick(4, 16, 40)), decay=[float(a) for a in 1 - rng.random(heads) * 0.2],
+                rot=dict(dims=dims, base=float(pick(10.0, 1e4, 1e6))))))
+        else:
+            kv, group = int(pick(1, 2, 3)), int(pick(1, 2, 4))
+            rkv, rgroup = int(pick(1, 2)), int(pick(1, 3))
+            dim = int(pick(8, 24, 32, 64))
+            layers.append(dict(type="parallel", mlp=mlp, mixer=dict(
+                left=dict(heads=kv * group, kv_heads=kv, dim=dim, vdim=int(pick(dim, 8, 48)),
+                          scale=float(pick(0.1, 0.35, dim ** -0.5)), mask=dict(size=int(pick(1, 2, 5, 33, 64, 65, 200)))),
+                left_scale=float(pick(1.0, 0.3, 1.7)),
+                right=dict(heads=rkv * rgroup, kv_heads=rkv, dim=int(pick(4, 12, 32)), vdim=int(pick(4, 20, 32)),
+                           conv=int(pick(1, 2, 4, 7)), decay_rank=int(pick(1, 4, 9)), gate_rank=int(pick(2, 8))),
+                right_scale=float(pick(1.0, 0.5, 2.0)))))
+    start = int(rng.integers(0, len(layers)))
+    stop = int(rng.integers(start + 1, len(layers) + 1))
+    return dict(architecture="Kikalix", vocab=int(pick(50, 257, 640)), width=width,
+                norm=dict(eps=float(pick(1e-5, 1e-6, 1e-3))), layers=layers,
+                loop=dict(start=start, stop=stop, times=int(pick(1, 2, 3))))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(engine, tmp_path, seed):
+    spec = dict(config=drawn_configuration(seed), seed=100 + seed, std=0.15)
+    folder = helpers.make_kikalix_dir(str(tmp_path / "free"), spec)
+    steady = helpers.make_kikalix_dir(str(tmp_path / "steady"), spec, steady_routing=True)
+    vocab = drawn_configuration(seed)["vocab"]
+    seqs = [helpers.random_tokens(seed * 10 + i, n, vocab) for i, n in enumerate([90, 7, 1])]
+    for path, dtype in ((folder, "float32"), (steady, "bfloat16")):
+        config, tensors = P.read_model(path)
+        refs = [P.forward(config, tensors, s).numpy() for s in seqs]
+        runner, cache, _ = open_runner(engine, path, dtype)
+        slots = [cache.open_slot() for _ in seqs]
+        heads = [max(1, len(s) - 12) for s in seqs]                      # prompts, then decoding together
+        out = runner.step([entry(sl, s[:n]) for sl, s, n in zip(slots, seqs, heads)])
+        got, row = [[] for _ in seqs], 0
+        for b, n in enumerate(heads):
+            got[b].append(out[row:row + n].clone())
+            row += n
+        for p in range(12):
+            live = [b for b in range(len(seqs)) if heads[b] + p < len(seqs[b])]
+            if not live:
+                break
+            out = runner.step([entry(slots[b], [seqs[b][heads[b] + p]]) for b in live])
+            for r, b in enumerate(live):
+                got[b].append(out[r:r + 1].clone())
+        for b in range(len(seqs)):
+            close(torch.cat(got[b]).cpu().numpy(), refs[b], dtype, f"drawn configuration {seed}, sequence {b}",
+                  drawn=True)
+        runner.check_device_status()

@@ -88,7 +88,7 @@ KIKALIX = {
                 mlp=_moe(24, 0.5, 3, 1)),
         ], loop=dict(start=1, stop=3, times=3)), seed=21, std=0.12),
     "K2": dict(
-        config=dict(architecture="Kikalix", vocab=512, width=256, norm=dict(eps=1e-5), layers=[
+        config=dict(architecture="Kikalix", vocab=512, width=320, norm=dict(eps=2e-5), layers=[
             dict(type="retention", mixer=dict(heads=4, dim=64, vdim=64, decay=[0.98, 0.99, 0.995, 0.999],
                                               rot=dict(dims=64, base=10000.0)), mlp=_moe(128, 2.0, 4, 2)),
             dict(type="parallel", mixer=dict(

@@ -574,7 +574,7 @@ def drawn_configuration(seed):
                 right_scale=float(pick(1.0, 0.5, 2.0)))))
     start = int(rng.integers(0, len(layers)))
     stop = int(rng.integers(start + 1, len(layers) + 1))
-    return dict(architecture="Kikalix", vocab=int(pick(50, 257, 640)), width=width,
+    return dict(architecture="Kikalix", vocab=int(pick(50, 257, 601)), width=width,
                 norm=dict(eps=float(pick(1e-5, 1e-6, 1e-3))), layers=layers,
                 loop=dict(start=start, stop=stop, times=int(pick(1, 2, 3))))
 

@@ -255,8 +255,8 @@ __global__ __launch_bounds__(256) void moe_experts_rows_kernel(
 
 // y[t, e, f] = weight(t, e) * act(gate, up) from gu [T, E, 2 ff] (an expert's ff gate columns, then
 // its ff up columns); weight(t, e) is the router's weight if token t chose expert e, else 0.
-template <typename A>
-__global__ void moe_dense_gate_kernel(const A* __restrict__ gu, const int* __restrict__ ids,
+template <typename G, typename A>
+__global__ void moe_dense_gate_kernel(const G* __restrict__ gu, const int* __restrict__ ids,
                                       const float* __restrict__ weights, A* __restrict__ y, int ff,
                                       int experts, int top, float limit, float alpha) {
   pdl_trigger();
@@ -281,19 +281,24 @@ __global__ void moe_dense_gate_kernel(const A* __restrict__ gu, const int* __res
 
 }  // namespace
 
-LRM_API int lrm_moe_dense_gate(const void* gu, int dtype, const int* ids, const float* weights, void* y,
-                               int tokens, int ff, int experts, int top, float limit, float alpha,
+// gu: float32 or the type of y (`gu_dtype`); y: `dtype`.
+LRM_API int lrm_moe_dense_gate(const void* gu, int gu_dtype, int dtype, const int* ids, const float* weights,
+                               void* y, int tokens, int ff, int experts, int top, float limit, float alpha,
                                cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (ff <= 0 || experts <= 0 || top <= 0 || top > experts) return LRM_BAD_ARGUMENT;
   const long long items = static_cast<long long>(experts) * ff;
   const dim3 grid(tokens, static_cast<unsigned>((items + 1023) / 1024));
-  if (dtype == LRM_BF16)
-    LRM_LAUNCH(moe_dense_gate_kernel<__nv_bfloat16>, grid, 256, 0, stream, static_cast<const __nv_bfloat16*>(gu),
+  if (dtype == LRM_BF16 && gu_dtype == LRM_BF16)
+    LRM_LAUNCH((moe_dense_gate_kernel<__nv_bfloat16, __nv_bfloat16>), grid, 256, 0, stream,
+               static_cast<const __nv_bfloat16*>(gu), ids, weights, static_cast<__nv_bfloat16*>(y), ff, experts, top,
+               limit, alpha);
+  else if (dtype == LRM_BF16 && gu_dtype == LRM_F32)
+    LRM_LAUNCH((moe_dense_gate_kernel<float, __nv_bfloat16>), grid, 256, 0, stream, static_cast<const float*>(gu),
                ids, weights, static_cast<__nv_bfloat16*>(y), ff, experts, top, limit, alpha);
-  else if (dtype == LRM_F32)
-    LRM_LAUNCH(moe_dense_gate_kernel<float>, grid, 256, 0, stream, static_cast<const float*>(gu), ids, weights,
-               static_cast<float*>(y), ff, experts, top, limit, alpha);
+  else if (dtype == LRM_F32 && gu_dtype == LRM_F32)
+    LRM_LAUNCH((moe_dense_gate_kernel<float, float>), grid, 256, 0, stream, static_cast<const float*>(gu), ids,
+               weights, static_cast<float*>(y), ff, experts, top, limit, alpha);
   else
     return LRM_BAD_ARGUMENT;
   return 0;

@@ -564,10 +564,10 @@ def moe_experts_rows(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor,
 
 
 def moe_dense_gate(gate_up: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, experts: int, limit: float,
-                   alpha: float) -> torch.Tensor:
+                   alpha: float, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """From every expert's gate and up for every token, [T, E * 2 ff] (an expert's ff gate columns,
-    then its ff up columns): y [T, E * ff] = weight(t, e) * act(gate, up), zero where token t did not
-    choose expert e."""
+    then its ff up columns; float32, or the output's type): y [T, E * ff] = weight(t, e) * act(gate,
+    up) in `out_dtype` (default: the input's), zero where token t did not choose expert e."""
     _check(gate_up, "gate_up", dims=2)
     _check(ids, "ids", torch.int32, 2)
     _check(weights, "weights", torch.float32, 2)
@@ -575,8 +575,9 @@ def moe_dense_gate(gate_up: torch.Tensor, ids: torch.Tensor, weights: torch.Tens
     if gate_up.shape[0] != T or gate_up.shape[1] % (2 * experts) or tuple(weights.shape) != (T, top):
         raise InvalidError("moe_dense_gate: shapes do not agree")
     ff = gate_up.shape[1] // (2 * experts)
-    y = _activation(T, experts * ff, gate_up.dtype, gate_up.device)
-    _done(_lib().lrm_moe_dense_gate(_ptr(gate_up), _code(gate_up.dtype), _ptr(ids), _ptr(weights), _ptr(y), T, ff,
+    out_dtype = out_dtype or gate_up.dtype
+    y = _activation(T, experts * ff, out_dtype, gate_up.device)
+    _done(_lib().lrm_moe_dense_gate(_ptr(gate_up), _code(gate_up.dtype), _code(out_dtype), _ptr(ids), _ptr(weights), _ptr(y), T, ff,
                                     experts, top, ctypes.c_float(limit), ctypes.c_float(alpha), _stream()),
           "moe_dense_gate")
     return y

@@ -99,7 +99,7 @@ WORK: Dict[str, Callable[..., Tuple[float, float]]] = {
         min(_v(a[8]) * _v(a[12]), _v(a[11])) * 3.0 * _v(a[10]) * _v(a[9]) * _ELEM[_v(a[4])]
         + 4.0 * _v(a[8]) * _v(a[12]) * _v(a[13]) * _v(a[9]),
         6.0 * _v(a[8]) * _v(a[12]) * _v(a[10]) * _v(a[9])),
-    "lrm_moe_dense_gate": lambda a: (3.0 * _v(a[5]) * _v(a[6]) * _v(a[7]) * _ELEM[_v(a[1])], 0),
+    "lrm_moe_dense_gate": lambda a: (_v(a[6]) * _v(a[7]) * _v(a[8]) * (2.0 * _ELEM[_v(a[1])] + _ELEM[_v(a[2])]), 0),
     "lrm_moe_router": lambda a: (_v(a[7]) * _v(a[8]) * _ELEM[_v(a[1])] + 4.0 * _v(a[9]) * _v(a[8]), 2.0 * _v(a[7]) * _v(a[8]) * _v(a[9])),
     "lrm_moe_route": lambda a: (_v(a[4]) * (_v(a[5]) * 4.0 + _v(a[6]) * 8.0), 0),
     "lrm_add_row": lambda a: (8.0 * _v(a[2]) * _v(a[3]), 0),

@@ -86,7 +86,9 @@ class MixtureOfExperts(FeedForward):
         ids, weights = self.route(x)
         if (x.dtype == torch.bfloat16 and self.gate_up.dtype == torch.bfloat16 and x.shape[0] >= self.DENSE_ROWS
                 and self.num_experts <= self.DENSE_RATIO * self.top):
-            y = ops.moe_dense_gate(self.gate_up_all(x), ids, weights, self.num_experts, self.limit, self.alpha)
+            # gate and up stay float32 up to the activation, as they do token by token
+            both = self.gate_up_all(x, out_dtype=torch.float32)
+            y = ops.moe_dense_gate(both, ids, weights, self.num_experts, self.limit, self.alpha, out_dtype=x.dtype)
             return self.down_all(y, epilogue=ops.ADD, out=residual, ctx=ctx)
         planes = ops.moe_experts_rows(x, self.gate_up, self.down, ids, weights, self.limit, self.alpha)
         if ctx.may_defer:

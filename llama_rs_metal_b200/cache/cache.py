@@ -47,6 +47,8 @@ class KeyValueView:
     head_dim: int
     window: Optional[int]
     group: int = 0  # index of the storage group (a step's destination rows are per group)
+    value_dim: Optional[int] = None  # head width of values (None: v's own)
+    values_in_keys: bool = False     # values are the first value_dim columns of the key rows; v is k
 
 
 @dataclass
@@ -68,7 +70,9 @@ class KeyValueGroup:
         # zeroed once: a kernel may load rows of a page that no token was ever stored in (they are
         # masked, but 0 x NaN would still be NaN)
         self.k = {e: torch.zeros(shape, dtype=dtype, device=device) for e in entries}
-        self.v = {e: torch.zeros(value_shape, dtype=dtype, device=device) for e in entries}
+        # values that live inside the key rows have no storage of their own
+        self.v = self.k if request.values_in_keys else \
+            {e: torch.zeros(value_shape, dtype=dtype, device=device) for e in entries}
 
     def first_kept_page(self, length: int) -> int:
         """Lowest logical page a sequence of `length` tokens still needs."""
@@ -137,7 +141,8 @@ class KeyValueGroup:
             self.dirty = False
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in list(self.k.values()) + list(self.v.values()))
+        tensors = list(self.k.values()) + ([] if self.request.values_in_keys else list(self.v.values()))
+        return sum(t.numel() * t.element_size() for t in tensors)
 
 
 class StateGroup:
@@ -376,7 +381,8 @@ class Cache:
         if kind == "kv":
             g = self.kv_groups[index]
             return KeyValueView(g.k[cell], g.v[cell], g.table_device, g.page_size,
-                                g.request.kv_heads, g.request.head_dim, g.request.window, index)
+                                g.request.kv_heads, g.request.head_dim, g.request.window, index,
+                                g.request.value_dim or g.request.head_dim, g.request.values_in_keys)
         if kind == "state":
             return StateView(self.state_groups[index].state[cell])
         return None
@@ -394,12 +400,13 @@ class Cache:
         n = self.length(slot)
         shape = (n, g.request.kv_heads, g.request.head_dim)
         k = torch.full(shape, float("nan"), dtype=torch.float32)
-        v = torch.full(shape[:2] + (g.request.value_dim or g.request.head_dim,), float("nan"), dtype=torch.float32)
+        dv = g.request.value_dim or g.request.head_dim
+        v = torch.full(shape[:2] + (dv,), float("nan"), dtype=torch.float32)
         for p in range(n):
             page = int(g.table_host[slot][p // g.page_size])
             if page >= 0:
                 k[p] = g.k[entry][page, :, p % g.page_size].float().cpu()
-                v[p] = g.v[entry][page, :, p % g.page_size].float().cpu()
+                v[p] = g.v[entry][page, :, p % g.page_size, :dv].float().cpu()
         return k, v
 
     def bytes(self) -> int:

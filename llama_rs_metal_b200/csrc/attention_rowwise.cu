@@ -15,7 +15,12 @@
 // float32 per query head) a key at distance n = p - j behind the query loses
 // slope_h * n from its score (a linear distance penalty, no rotation needed);
 // `out_scale` multiplies the result before it is rounded (a mixer whose output
-// enters a weighted sum of mixers).
+// enters a weighted sum of mixers). With `sinks` (one float32 per query head) the softmax's
+// denominator also holds exp(sink_h): a key that is always seen, with no value, whose score is
+// not scaled. With a query temperature (`temp_every` > 0) the query at position p counts
+// 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) times (the factor goes into the score's
+// scale, in float32). `v_stride` is the distance between two value rows in elements: values
+// that are the first dv columns of the key rows are read from the keys' storage with the keys' d.
 #include "common.cuh"
 
 constexpr int kMaxPerLane = 16;  // head_dim <= 512
@@ -24,12 +29,12 @@ struct PackedKeys {
   const void* k;
   const void* v;
   size_t base;  // index of the sequence's first packed token
-  int kv_heads, d, dv;
+  int kv_heads, d, vs;
   template <typename A> __device__ const A* key(int p, int kh) const {
     return static_cast<const A*>(k) + ((base + p) * kv_heads + kh) * d;
   }
   template <typename A> __device__ const A* value(int p, int kh) const {
-    return static_cast<const A*>(v) + ((base + p) * kv_heads + kh) * dv;
+    return static_cast<const A*>(v) + ((base + p) * kv_heads + kh) * vs;
   }
 };
 
@@ -37,21 +42,21 @@ struct PagedKeys {
   const void* k;
   const void* v;
   const int* table;  // this slot's row of the page table
-  int kv_heads, d, dv, page_size;
+  int kv_heads, d, vs, page_size;
   template <typename A> __device__ const A* key(int p, int kh) const {
     const size_t page = table[p / page_size];
     return static_cast<const A*>(k) + ((page * kv_heads + kh) * page_size + p % page_size) * d;
   }
   template <typename A> __device__ const A* value(int p, int kh) const {
     const size_t page = table[p / page_size];
-    return static_cast<const A*>(v) + ((page * kv_heads + kh) * page_size + p % page_size) * dv;
+    return static_cast<const A*>(v) + ((page * kv_heads + kh) * page_size + p % page_size) * vs;
   }
 };
 
 template <typename A, typename Keys>
 __device__ void attend_row(const A* __restrict__ q, A* __restrict__ out, const Keys& keys, int kh,
                            int first, int last, int d, int dv, float scale, float slope,
-                           float out_scale) {
+                           float out_scale, float sink) {
   const int lane = threadIdx.x & 31;
   float qv[kMaxPerLane], acc[kMaxPerLane];
 #pragma unroll
@@ -60,7 +65,8 @@ __device__ void attend_row(const A* __restrict__ q, A* __restrict__ out, const K
     qv[i] = j < d ? to_f32(q[j]) : 0.f;
     acc[i] = 0.f;
   }
-  float m = -INFINITY, l = 0.f;
+  // a sink is a key met before all others: score `sink`, weight 1 at its own maximum, no value
+  float m = sink, l = sink > -INFINITY ? 1.f : 0.f;
   for (int p = first; p <= last; ++p) {
     const A* kr = keys.template key<A>(p, kh);
     const A* vr = keys.template value<A>(p, kh);
@@ -89,21 +95,28 @@ __device__ void attend_row(const A* __restrict__ q, A* __restrict__ out, const K
   }
 }
 
+__device__ __forceinline__ float query_temperature(int pos, float coef, int every) {
+  return every > 0 ? 1.0f + coef * logf(static_cast<float>((pos + 1) / every + 1)) : 1.0f;
+}
+
 template <typename A>
 __global__ void attention_packed_kernel(const A* __restrict__ q, const A* __restrict__ k,
                                         const A* __restrict__ v, A* __restrict__ out,
                                         const int* __restrict__ cu_seqlens,
                                         const int* __restrict__ seq_of_token, int q_heads,
                                         int kv_heads, int d, int dv, float scale, int window,
-                                        const float* __restrict__ slopes, float out_scale) {
+                                        const float* __restrict__ slopes, float out_scale,
+                                        const float* __restrict__ sinks, float temp_coef,
+                                        int temp_every, int v_stride) {
   const int t = blockIdx.x, h = blockIdx.y;
   const int start = cu_seqlens[seq_of_token[t]];
   const int pos = t - start;
   const int first = window > 0 ? max(0, pos - window + 1) : 0;
-  PackedKeys keys{k, v, static_cast<size_t>(start), kv_heads, d, dv};
+  PackedKeys keys{k, v, static_cast<size_t>(start), kv_heads, d, v_stride};
   const size_t row = static_cast<size_t>(t) * q_heads + h;
-  attend_row<A>(q + row * d, out + row * dv, keys, h / (q_heads / kv_heads), first, pos, d, dv, scale,
-                slopes != nullptr ? slopes[h] : 0.f, out_scale);
+  attend_row<A>(q + row * d, out + row * dv, keys, h / (q_heads / kv_heads), first, pos, d, dv,
+                scale * query_temperature(pos, temp_coef, temp_every),
+                slopes != nullptr ? slopes[h] : 0.f, out_scale, sinks != nullptr ? sinks[h] : -INFINITY);
 }
 
 template <typename A>
@@ -115,7 +128,9 @@ __global__ void attention_paged_kernel(const A* __restrict__ q, const A* __restr
                                        const int* __restrict__ seq_of_token,
                                        const int* __restrict__ positions, int q_heads, int kv_heads,
                                        int d, int dv, int page_size, float scale, int window,
-                                       const float* __restrict__ slopes, float out_scale) {
+                                       const float* __restrict__ slopes, float out_scale,
+                                       const float* __restrict__ sinks, float temp_coef,
+                                       int temp_every, int v_stride) {
   // query t of the step belongs to sequence b and stands at position pos; without the two
   // arrays there is one query per sequence, its newest token
   const int t = blockIdx.x, h = blockIdx.y;
@@ -123,10 +138,11 @@ __global__ void attention_paged_kernel(const A* __restrict__ q, const A* __restr
   const int pos = positions != nullptr ? positions[t] : kv_lens[b] - 1;
   const int first = window > 0 ? max(0, pos - window + 1) : 0;
   PagedKeys keys{k_pages, v_pages, page_table + static_cast<size_t>(slots[b]) * table_stride,
-                 kv_heads, d, dv, page_size};
+                 kv_heads, d, v_stride, page_size};
   const size_t row = static_cast<size_t>(t) * q_heads + h;
-  attend_row<A>(q + row * d, out + row * dv, keys, h / (q_heads / kv_heads), first, pos, d, dv, scale,
-                slopes != nullptr ? slopes[h] : 0.f, out_scale);
+  attend_row<A>(q + row * d, out + row * dv, keys, h / (q_heads / kv_heads), first, pos, d, dv,
+                scale * query_temperature(pos, temp_coef, temp_every),
+                slopes != nullptr ? slopes[h] : 0.f, out_scale, sinks != nullptr ? sinks[h] : -INFINITY);
 }
 
 static bool bad_geometry(int q_heads, int kv_heads, int d, int dv) {
@@ -138,8 +154,10 @@ LRM_API int lrm_attention_packed_rowwise(const void* q, const void* k, const voi
                                          int dtype, const int* cu_seqlens, const int* seq_of_token,
                                          int tokens, int q_heads, int kv_heads, int d, int dv,
                                          float scale, int window, const float* slopes,
-                                         float out_scale, cudaStream_t stream) {
+                                         float out_scale, const float* sinks, float temp_coef,
+                                         int temp_every, int v_stride, cudaStream_t stream) {
   if (tokens <= 0) return 0;
+  if (v_stride <= 0) v_stride = dv;
   if (bad_geometry(q_heads, kv_heads, d, dv)) return LRM_BAD_ARGUMENT;
   if (q_heads > 65535) return LRM_UNSUPPORTED;
   const dim3 grid(tokens, q_heads);
@@ -147,12 +165,13 @@ LRM_API int lrm_attention_packed_rowwise(const void* q, const void* k, const voi
     attention_packed_kernel<float><<<grid, 32, 0, stream>>>(
         static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v),
         static_cast<float*>(out), cu_seqlens, seq_of_token, q_heads, kv_heads, d, dv, scale, window,
-        slopes, out_scale);
+        slopes, out_scale, sinks, temp_coef, temp_every, v_stride);
   else if (dtype == LRM_BF16)
     attention_packed_kernel<__nv_bfloat16><<<grid, 32, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
         static_cast<const __nv_bfloat16*>(v), static_cast<__nv_bfloat16*>(out), cu_seqlens,
-        seq_of_token, q_heads, kv_heads, d, dv, scale, window, slopes, out_scale);
+        seq_of_token, q_heads, kv_heads, d, dv, scale, window, slopes, out_scale, sinks, temp_coef,
+        temp_every, v_stride);
   else
     return LRM_BAD_ARGUMENT;
   LRM_LAUNCH_CHECK();
@@ -168,8 +187,10 @@ LRM_API int lrm_attention_paged_rowwise(const void* q, const void* k_pages, cons
                                         const int* seq_of_token, const int* positions,
                                         int queries, int q_heads, int kv_heads, int d, int dv,
                                         int page_size, float scale, int window, const float* slopes,
-                                        float out_scale, cudaStream_t stream) {
+                                        float out_scale, const float* sinks, float temp_coef,
+                                        int temp_every, int v_stride, cudaStream_t stream) {
   if (queries <= 0) return 0;
+  if (v_stride <= 0) v_stride = dv;
   if (bad_geometry(q_heads, kv_heads, d, dv) || page_size <= 0) return LRM_BAD_ARGUMENT;
   if ((seq_of_token == nullptr) != (positions == nullptr)) return LRM_BAD_ARGUMENT;
   if (positions == nullptr && kv_lens == nullptr) return LRM_BAD_ARGUMENT;
@@ -180,13 +201,13 @@ LRM_API int lrm_attention_paged_rowwise(const void* q, const void* k_pages, cons
         static_cast<const float*>(q), static_cast<const float*>(k_pages),
         static_cast<const float*>(v_pages), static_cast<float*>(out), page_table, table_stride,
         slots, kv_lens, seq_of_token, positions, q_heads, kv_heads, d, dv, page_size, scale, window,
-        slopes, out_scale);
+        slopes, out_scale, sinks, temp_coef, temp_every, v_stride);
   else if (dtype == LRM_BF16)
     attention_paged_kernel<__nv_bfloat16><<<grid, 32, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
         static_cast<const __nv_bfloat16*>(v_pages), static_cast<__nv_bfloat16*>(out), page_table,
         table_stride, slots, kv_lens, seq_of_token, positions, q_heads, kv_heads, d, dv, page_size,
-        scale, window, slopes, out_scale);
+        scale, window, slopes, out_scale, sinks, temp_coef, temp_every, v_stride);
   else
     return LRM_BAD_ARGUMENT;
   LRM_LAUNCH_CHECK();

@@ -24,9 +24,17 @@
 // product. Head sizes 32, 64 and 128; other sizes use the row-wise kernel.
 // With `slopes` (float32 per query head) a key n positions behind its query loses slope * n from
 // its score (a linear distance penalty); `out_scale` multiplies the result before it is rounded.
+// With `sinks` (float32 per query head) exp(sink_h) joins the softmax's denominator: a row starts
+// from the running maximum sink_h and the mass 1 instead of -inf and 0 (decode: the merge of the
+// splits counts the sink as one more part). With `temp_every` > 0 the query at position p counts
+// 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) times: the factor goes into the row's scale.
 #include "attention_mma.cuh"
 
 namespace {
+
+__device__ __forceinline__ float query_temperature(int pos, float coef, int every) {
+  return every > 0 ? 1.0f + coef * logf(static_cast<float>((pos + 1) / every + 1)) : 1.0f;
+}
 
 // --------------------------------------------------------------------------- prefill
 template <int D>
@@ -34,7 +42,8 @@ __global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
     const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ out,
     const int* __restrict__ cu_seqlens, int q_heads, int kv_heads, float scale_log2, int window,
-    const float* __restrict__ slopes, float out_scale) {
+    const float* __restrict__ slopes, float out_scale, const float* __restrict__ sinks, float temp_coef,
+    int temp_every) {
   constexpr int STRIDE = D + 8, TILE = kTile * STRIDE;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2][64][STRIDE]
@@ -61,7 +70,12 @@ __global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
   for (int dn = 0; dn < D / 8; ++dn)
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[dn][e] = 0.f;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  // a sink: the row's softmax starts from the maximum sink and the mass 1 (held by one lane of four)
+  const float sink_log2 = sinks != nullptr ? sinks[h] * 1.4426950408889634f : -INFINITY;
+  const float l0 = (sinks != nullptr && t == 0) ? 1.f : 0.f;
+  float m[2] = {sink_log2, sink_log2}, l[2] = {l0, l0};
+  const float scale_row[2] = {scale_log2 * query_temperature(row0 + g, temp_coef, temp_every),
+                              scale_log2 * query_temperature(row0 + g + 8, temp_coef, temp_every)};
 
   const int kt_first = window > 0 ? max(0, q0 - window + 1) / kTile : 0;
   const int kt_last = qt;
@@ -95,7 +109,7 @@ __global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
         const int key = kt * kTile + 8 * nt + 2 * t + (e & 1);
         const int query = row0 + g + 8 * (e >> 1);
         const bool visible = key <= query && (window <= 0 || key > query - window);
-        s[nt][e] = visible ? s[nt][e] * scale_log2 - slope_log2 * static_cast<float>(query - key) : -INFINITY;
+        s[nt][e] = visible ? s[nt][e] * scale_row[e >> 1] - slope_log2 * static_cast<float>(query - key) : -INFINITY;
       }
     }
     softmax_update<D, 8>(s, o, m, l);
@@ -129,7 +143,8 @@ __global__ __launch_bounds__(kThreads) void attention_extend_tiled_kernel(
     const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out,
     const int* __restrict__ cu_seqlens, const int* __restrict__ page_table, int table_stride,
     const int* __restrict__ slots, const int* __restrict__ kv_lens, int q_heads, int kv_heads,
-    float scale_log2, int window, const float* __restrict__ slopes, float out_scale) {
+    float scale_log2, int window, const float* __restrict__ slopes, float out_scale,
+    const float* __restrict__ sinks, float temp_coef, int temp_every) {
   constexpr int STRIDE = D + 8, TILE = kTile * STRIDE;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2][64][STRIDE]
@@ -156,7 +171,11 @@ __global__ __launch_bounds__(kThreads) void attention_extend_tiled_kernel(
   for (int dn = 0; dn < D / 8; ++dn)
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[dn][e] = 0.f;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const float sink_log2 = sinks != nullptr ? sinks[h] * 1.4426950408889634f : -INFINITY;
+  const float l0 = (sinks != nullptr && t == 0) ? 1.f : 0.f;
+  float m[2] = {sink_log2, sink_log2}, l[2] = {l0, l0};
+  const float scale_row[2] = {scale_log2 * query_temperature(before + row0 + g, temp_coef, temp_every),
+                              scale_log2 * query_temperature(before + row0 + g + 8, temp_coef, temp_every)};
 
   // keys the tile's queries see: from the first query's window to the last query's own position
   const int first_key = window > 0 ? max(0, before + q0 - window + 1) : 0;
@@ -195,7 +214,7 @@ __global__ __launch_bounds__(kThreads) void attention_extend_tiled_kernel(
         const int key = kt * kTile + 8 * nt + 2 * t + (e & 1);
         const int query = before + row0 + g + 8 * (e >> 1);  // position in the sequence
         const bool visible = key <= query && (window <= 0 || key > query - window);
-        s[nt][e] = visible ? s[nt][e] * scale_log2 - slope_log2 * static_cast<float>(query - key) : -INFINITY;
+        s[nt][e] = visible ? s[nt][e] * scale_row[e >> 1] - slope_log2 * static_cast<float>(query - key) : -INFINITY;
       }
     }
     softmax_update<D, 8>(s, o, m, l);
@@ -227,7 +246,7 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
     const __nv_bfloat16* __restrict__ v_pages, float* __restrict__ partials,
     const int* __restrict__ page_table, int table_stride, const int* __restrict__ slots,
     const int* __restrict__ kv_lens, int q_heads, int kv_heads, int row_groups, float scale_log2,
-    int window, int n_splits, const float* __restrict__ slopes) {
+    int window, int n_splits, const float* __restrict__ slopes, float temp_coef, int temp_every) {
   // no early griddepcontrol.launch_dependents: the kernels after attention trigger at once in their
   // turn, and a whole layer's kernels scheduled behind a running attention made decode steps slower
   constexpr int STRIDE = D + 8, TILE = kTile * STRIDE;
@@ -244,6 +263,7 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 
   const int len = kv_lens[b];
+  scale_log2 *= query_temperature(len - 1, temp_coef, temp_every);  // every query stands at len - 1
   // the distance penalty of the two query heads (rows g and g + 8 of the tile) this thread holds
   float slope_log2[2] = {0.f, 0.f};
   if (slopes != nullptr) {
@@ -360,12 +380,15 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
 // Branch-free and in chunks of 8 parts, so that a chunk's loads are all in flight together.
 template <int D>
 __global__ void attention_merge_kernel(const float* __restrict__ partials,
-                                       __nv_bfloat16* __restrict__ out, int n_parts, float out_scale) {
+                                       __nv_bfloat16* __restrict__ out, int n_parts, float out_scale,
+                                       const float* __restrict__ sinks, int q_heads) {
+  // a sink is one more part: maximum sink_h, mass 1, nothing accumulated
+  const float sink_log2 = sinks != nullptr ? sinks[blockIdx.x % q_heads] * 1.4426950408889634f : -INFINITY;
   pdl_trigger();  // a small kernel: let the next one start (and prefetch its weights) right away
   pdl_wait();
   const float* src = partials + static_cast<size_t>(blockIdx.x) * n_parts * (D + 2);
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float M = -INFINITY;
+    float M = sink_log2;
     for (int i0 = 0; i0 < n_parts; i0 += 8) {
       float mi[8];
 #pragma unroll
@@ -373,7 +396,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ partials,
 #pragma unroll
       for (int u = 0; u < 8; ++u) M = fmaxf(M, mi[u]);
     }
-    float acc = 0.f, mass = 0.f;
+    float acc = 0.f, mass = sink_log2 == -INFINITY ? 0.f : exp2f(sink_log2 - M);
     for (int i0 = 0; i0 < n_parts; i0 += 8) {
       float mi[8], ai[8], li[8];
 #pragma unroll
@@ -399,7 +422,8 @@ __global__ void attention_merge_kernel(const float* __restrict__ partials,
 template <int D> int prefill_launch(const void* q, const void* k, const void* v, void* out,
                                     const int* cu_seqlens, int seqs, int max_seq_len, int q_heads,
                                     int kv_heads, float scale, int window, const float* slopes,
-                                    float out_scale, cudaStream_t stream) {
+                                    float out_scale, const float* sinks, float temp_coef, int temp_every,
+                                    cudaStream_t stream) {
   const int smem = 4 * kTile * (D + 8) * 2;
   auto kernel = attention_prefill_tiled_kernel<D>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -409,7 +433,7 @@ template <int D> int prefill_launch(const void* q, const void* k, const void* v,
   LRM_LAUNCH(kernel, grid, kThreads, smem, stream, static_cast<const __nv_bfloat16*>(q),
              static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
              static_cast<__nv_bfloat16*>(out), cu_seqlens, q_heads, kv_heads,
-             scale * 1.4426950408889634f, window, slopes, out_scale);
+             scale * 1.4426950408889634f, window, slopes, out_scale, sinks, temp_coef, temp_every);
   return 0;
 }
 
@@ -417,7 +441,8 @@ template <int D> int extend_launch(const void* q, const void* k_pages, const voi
                                    const int* cu_seqlens, const int* page_table, int table_stride,
                                    const int* slots, const int* kv_lens, int seqs, int max_seq_len,
                                    int q_heads, int kv_heads, float scale, int window, const float* slopes,
-                                   float out_scale, cudaStream_t stream) {
+                                   float out_scale, const float* sinks, float temp_coef, int temp_every,
+                                   cudaStream_t stream) {
   const int smem = 4 * kTile * (D + 8) * 2;
   auto kernel = attention_extend_tiled_kernel<D>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -427,7 +452,8 @@ template <int D> int extend_launch(const void* q, const void* k_pages, const voi
   LRM_LAUNCH(kernel, grid, kThreads, smem, stream, static_cast<const __nv_bfloat16*>(q),
              static_cast<const __nv_bfloat16*>(k_pages), static_cast<const __nv_bfloat16*>(v_pages),
              static_cast<__nv_bfloat16*>(out), cu_seqlens, page_table, table_stride, slots, kv_lens,
-             q_heads, kv_heads, scale * 1.4426950408889634f, window, slopes, out_scale);
+             q_heads, kv_heads, scale * 1.4426950408889634f, window, slopes, out_scale, sinks, temp_coef,
+             temp_every);
   return 0;
 }
 
@@ -435,7 +461,8 @@ template <int D> int decode_launch(const void* q, const void* k_pages, const voi
                                    float* partials, void* out, const int* page_table,
                                    int table_stride, const int* slots, const int* kv_lens, int seqs,
                                    int q_heads, int kv_heads, float scale, int window, int n_splits,
-                                   const float* slopes, float out_scale, cudaStream_t stream) {
+                                   const float* slopes, float out_scale, const float* sinks, float temp_coef,
+                                   int temp_every, cudaStream_t stream) {
   const int smem = 4 * kTile * (D + 8) * 2;
   auto kernel = attention_decode_tiled_kernel<D>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -445,9 +472,9 @@ template <int D> int decode_launch(const void* q, const void* k_pages, const voi
   LRM_LAUNCH(kernel, grid, kThreads, smem, stream, static_cast<const __nv_bfloat16*>(q),
              static_cast<const __nv_bfloat16*>(k_pages), static_cast<const __nv_bfloat16*>(v_pages),
              partials, page_table, table_stride, slots, kv_lens, q_heads, kv_heads, row_groups,
-             scale * 1.4426950408889634f, window, n_splits, slopes);
+             scale * 1.4426950408889634f, window, n_splits, slopes, temp_coef, temp_every);
   LRM_LAUNCH(attention_merge_kernel<D>, seqs * q_heads, D <= 64 ? 64 : 128, 0, stream, partials,
-             static_cast<__nv_bfloat16*>(out), n_splits, out_scale);
+             static_cast<__nv_bfloat16*>(out), n_splits, out_scale, sinks, q_heads);
   return 0;
 }
 
@@ -461,14 +488,15 @@ LRM_API int lrm_attention_tiled_supports(int head_dim, int page_size) {
 LRM_API int lrm_attention_prefill_tiled(const void* q, const void* k, const void* v, void* out,
                                         const int* cu_seqlens, int seqs, int max_seq_len,
                                         int q_heads, int kv_heads, int d, float scale, int window,
-                                        const float* slopes, float out_scale, cudaStream_t stream) {
+                                        const float* slopes, float out_scale, const float* sinks,
+                                        float temp_coef, int temp_every, cudaStream_t stream) {
   if (seqs <= 0 || max_seq_len <= 0) return 0;
   if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0) return LRM_BAD_ARGUMENT;
   if (q_heads > 65535 || seqs > 65535) return LRM_UNSUPPORTED;
   switch (d) {
-    case 32: return prefill_launch<32>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, stream);
-    case 64: return prefill_launch<64>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, stream);
-    case 128: return prefill_launch<128>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, stream);
+    case 32: return prefill_launch<32>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, sinks, temp_coef, temp_every, stream);
+    case 64: return prefill_launch<64>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, sinks, temp_coef, temp_every, stream);
+    case 128: return prefill_launch<128>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, sinks, temp_coef, temp_every, stream);
     default: return LRM_UNSUPPORTED;
   }
 }
@@ -480,15 +508,15 @@ LRM_API int lrm_attention_extend_tiled(const void* q, const void* k_pages, const
                                        const int* cu_seqlens, const int* page_table, int table_stride,
                                        const int* slots, const int* kv_lens, int seqs, int max_seq_len,
                                        int q_heads, int kv_heads, int d, int page_size, float scale,
-                                       int window, const float* slopes, float out_scale,
-                                       cudaStream_t stream) {
+                                       int window, const float* slopes, float out_scale, const float* sinks,
+                                       float temp_coef, int temp_every, cudaStream_t stream) {
   if (seqs <= 0 || max_seq_len <= 0) return 0;
   if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0) return LRM_BAD_ARGUMENT;
   if (q_heads > 65535 || seqs > 65535 || page_size != kTile) return LRM_UNSUPPORTED;
   switch (d) {
-    case 32: return extend_launch<32>(q, k_pages, v_pages, out, cu_seqlens, page_table, table_stride, slots, kv_lens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, stream);
-    case 64: return extend_launch<64>(q, k_pages, v_pages, out, cu_seqlens, page_table, table_stride, slots, kv_lens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, stream);
-    case 128: return extend_launch<128>(q, k_pages, v_pages, out, cu_seqlens, page_table, table_stride, slots, kv_lens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, stream);
+    case 32: return extend_launch<32>(q, k_pages, v_pages, out, cu_seqlens, page_table, table_stride, slots, kv_lens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, sinks, temp_coef, temp_every, stream);
+    case 64: return extend_launch<64>(q, k_pages, v_pages, out, cu_seqlens, page_table, table_stride, slots, kv_lens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, sinks, temp_coef, temp_every, stream);
+    case 128: return extend_launch<128>(q, k_pages, v_pages, out, cu_seqlens, page_table, table_stride, slots, kv_lens, seqs, max_seq_len, q_heads, kv_heads, scale, window, slopes, out_scale, sinks, temp_coef, temp_every, stream);
     default: return LRM_UNSUPPORTED;
   }
 }
@@ -500,16 +528,17 @@ LRM_API int lrm_attention_decode_tiled(const void* q, const void* k_pages, const
                                        int table_stride, const int* slots, const int* kv_lens,
                                        int seqs, int q_heads, int kv_heads, int d, int page_size,
                                        float scale, int window, int n_splits, const float* slopes,
-                                       float out_scale, cudaStream_t stream) {
+                                       float out_scale, const float* sinks, float temp_coef, int temp_every,
+                                       cudaStream_t stream) {
   if (seqs <= 0) return 0;
   if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || n_splits <= 0 ||
       partials == nullptr)
     return LRM_BAD_ARGUMENT;
   if (page_size != kTile || n_splits > 65535) return LRM_UNSUPPORTED;
   switch (d) {
-    case 32: return decode_launch<32>(q, k_pages, v_pages, partials, out, page_table, table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, window, n_splits, slopes, out_scale, stream);
-    case 64: return decode_launch<64>(q, k_pages, v_pages, partials, out, page_table, table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, window, n_splits, slopes, out_scale, stream);
-    case 128: return decode_launch<128>(q, k_pages, v_pages, partials, out, page_table, table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, window, n_splits, slopes, out_scale, stream);
+    case 32: return decode_launch<32>(q, k_pages, v_pages, partials, out, page_table, table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, window, n_splits, slopes, out_scale, sinks, temp_coef, temp_every, stream);
+    case 64: return decode_launch<64>(q, k_pages, v_pages, partials, out, page_table, table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, window, n_splits, slopes, out_scale, sinks, temp_coef, temp_every, stream);
+    case 128: return decode_launch<128>(q, k_pages, v_pages, partials, out, page_table, table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, window, n_splits, slopes, out_scale, sinks, temp_coef, temp_every, stream);
     default: return LRM_UNSUPPORTED;
   }
 }
@@ -569,7 +598,7 @@ LRM_API int lrm_attention_decode_tiled_static_scratch(const void* q, const void*
   // reads it, so nothing in the array needs clearing between calls.
   return lrm_attention_decode_tiled(q, k_pages, v_pages, partials, out, page_table, table_stride,
                                     slots, kv_lens, seqs, q_heads, kv_heads, head_dim, page_size,
-                                    scale, window, n_splits, nullptr, 1.0f, stream);
+                                    scale, window, n_splits, nullptr, 1.0f, nullptr, 0.f, 0, stream);
 }
 
 LRM_API const char* lrm_attention_static_scratch_error(int code) {

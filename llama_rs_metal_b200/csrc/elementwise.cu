@@ -17,6 +17,24 @@ __global__ void silu_mul_kernel(const A* __restrict__ gate_up, A* __restrict__ o
   out[idx] = from_f32<A>(g / (1.0f + expf(-g)) * u);
 }
 
+// The clamped gate: g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g * sigmoid(alpha * g) * (u + 1), from the same column layout. The input may be float32
+// while the output has the activation type (a product that keeps its sums until the activation).
+template <typename S, typename A>
+__global__ void clamped_gate_mul_kernel(const S* __restrict__ gate_up, A* __restrict__ out, size_t total,
+                                        int inter, int block, float limit, float alpha) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (idx >= total) return;
+  const size_t t = idx / inter;
+  const int c = static_cast<int>(idx % inter);
+  const size_t base = t * 2 * inter + static_cast<size_t>(c / block) * 2 * block + c % block;
+  const float g = fminf(to_f32(gate_up[base]), limit);
+  const float u = fminf(fmaxf(to_f32(gate_up[base + block]), -limit), limit);
+  out[idx] = from_f32<A>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+}
+
 template <typename D>
 __global__ void add_inplace_kernel(float* __restrict__ x, const D* __restrict__ delta, size_t n) {
   const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
@@ -59,6 +77,27 @@ LRM_API int lrm_silu_mul(const void* gate_up, void* out, int dtype, long long ro
   else
     return LRM_BAD_ARGUMENT;
   LRM_LAUNCH_CHECK();
+  return 0;
+}
+
+LRM_API int lrm_clamped_gate_mul(const void* gate_up, int in_dtype, void* out, int out_dtype, long long rows,
+                                 int inter, int block, float limit, float alpha, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (inter <= 0 || block <= 0 || inter % block != 0) return LRM_BAD_ARGUMENT;
+  const size_t total = static_cast<size_t>(rows) * inter;
+  if (in_dtype == LRM_F32 && out_dtype == LRM_F32)
+    LRM_LAUNCH((clamped_gate_mul_kernel<float, float>), blocks_for(total), 256, 0, stream,
+               static_cast<const float*>(gate_up), static_cast<float*>(out), total, inter, block, limit, alpha);
+  else if (in_dtype == LRM_F32 && out_dtype == LRM_BF16)
+    LRM_LAUNCH((clamped_gate_mul_kernel<float, __nv_bfloat16>), blocks_for(total), 256, 0, stream,
+               static_cast<const float*>(gate_up), static_cast<__nv_bfloat16*>(out), total, inter, block, limit,
+               alpha);
+  else if (in_dtype == LRM_BF16 && out_dtype == LRM_BF16)
+    LRM_LAUNCH((clamped_gate_mul_kernel<__nv_bfloat16, __nv_bfloat16>), blocks_for(total), 256, 0, stream,
+               static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), total, inter, block,
+               limit, alpha);
+  else
+    return LRM_BAD_ARGUMENT;
   return 0;
 }
 

@@ -295,6 +295,86 @@ LRM_API int lrm_rms_norm(float* x, const void* w, int w_dtype, void* out, int ou
 #undef LRM_NORM
 }
 
+// A norm behind a sublayer: stream[t] += mult * (y[t] / sqrt(mean(y[t]^2) + eps)) * w, with y the
+// sublayer's float32 output and `stream` the float32 residual stream, updated in place. With a
+// second weight `w2` the updated row is normalized once more in the same pass (the norm in front
+// of the next sublayer): out2[t] = stream[t] / sqrt(mean(stream[t]^2) + eps2) * w2. A thread
+// keeps its PER elements of the row in registers between the passes.
+template <typename W, typename O, int PER>
+__global__ void rms_norm_add_kernel(float* __restrict__ stream, const float* __restrict__ y,
+                                    const W* __restrict__ w, float mult, float eps, const W* __restrict__ w2,
+                                    O* __restrict__ out2, float eps2, int hidden) {
+  __shared__ float scratch[32];
+  float wv[PER], w2v[PER];
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {  // weights do not depend on the kernel before this one
+    const int i = threadIdx.x + e * blockDim.x;
+    wv[e] = i < hidden ? to_f32(w[i]) : 0.f;
+    w2v[e] = (w2 != nullptr && i < hidden) ? to_f32(w2[i]) : 0.f;
+  }
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = static_cast<size_t>(blockIdx.x) * hidden;
+  float yv[PER];
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const int i = threadIdx.x + e * blockDim.x;
+    yv[e] = i < hidden ? y[row + i] : 0.f;
+    ss = fmaf(yv[e], yv[e], ss);
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / static_cast<float>(hidden) + eps);
+  float ss2 = 0.f;
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const int i = threadIdx.x + e * blockDim.x;
+    if (i < hidden) {
+      const float v = stream[row + i] + mult * ((yv[e] * inv) * wv[e]);
+      stream[row + i] = v;
+      yv[e] = v;
+      ss2 = fmaf(v, v, ss2);
+    }
+  }
+  if (w2 == nullptr) return;
+  const float inv2 = 1.0f / sqrtf(block_sum(ss2, scratch) / static_cast<float>(hidden) + eps2);
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const int i = threadIdx.x + e * blockDim.x;
+    if (i < hidden) out2[row + i] = from_f32<O>((yv[e] * inv2) * w2v[e]);
+  }
+}
+
+template <typename W, typename O>
+static int launch_norm_add(float* stream, const float* y, const void* w, float mult, float eps, const void* w2,
+                           void* out2, float eps2, int n_rows, int hidden, cudaStream_t stream_handle) {
+  const int threads = hidden > 2048 ? 1024 : (hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 32));
+  const int per = (hidden + threads - 1) / threads;
+#define LRM_NORM_ADD(PER)                                                                                  \
+  return static_cast<int>(lrm_launch(rms_norm_add_kernel<W, O, PER>, n_rows, threads, 0, stream_handle,   \
+                                     stream, y, static_cast<const W*>(w), mult, eps,                       \
+                                     static_cast<const W*>(w2), static_cast<O*>(out2), eps2, hidden))
+  if (per <= 8) LRM_NORM_ADD(8);
+  if (per <= 32) LRM_NORM_ADD(32);
+  return LRM_UNSUPPORTED;  // rows longer than 32768 elements
+#undef LRM_NORM_ADD
+}
+
+LRM_API int lrm_rms_norm_add(float* stream, const float* y, const void* w, int w_dtype, float mult, float eps,
+                             const void* w2, void* out2, int out_dtype, float eps2, int n_rows, int hidden,
+                             cudaStream_t stream_handle) {
+  if (n_rows <= 0) return 0;
+  if (hidden <= 0 || !(eps > 0.f) || stream == nullptr || y == nullptr || w == nullptr) return LRM_BAD_ARGUMENT;
+  if ((w2 == nullptr) != (out2 == nullptr) || (w2 != nullptr && !(eps2 > 0.f))) return LRM_BAD_ARGUMENT;
+#define LRM_NORM_ADD_OF(WT, OT) \
+  launch_norm_add<WT, OT>(stream, y, w, mult, eps, w2, out2, eps2, n_rows, hidden, stream_handle)
+  if (w_dtype == LRM_F32 && out_dtype == LRM_F32) return LRM_NORM_ADD_OF(float, float);
+  if (w_dtype == LRM_F32 && out_dtype == LRM_BF16) return LRM_NORM_ADD_OF(float, __nv_bfloat16);
+  if (w_dtype == LRM_BF16 && out_dtype == LRM_F32) return LRM_NORM_ADD_OF(__nv_bfloat16, float);
+  if (w_dtype == LRM_BF16 && out_dtype == LRM_BF16) return LRM_NORM_ADD_OF(__nv_bfloat16, __nv_bfloat16);
+  return LRM_BAD_ARGUMENT;
+#undef LRM_NORM_ADD_OF
+}
+
 // Tuning and tests: 0 leaves the choice between one CTA and a cluster per row to the kernel's rule,
 // 1 never uses a cluster, 2, 4 or 8 always use one of that size (where the output is bfloat16).
 LRM_API void lrm_set_norm_ranks(int ranks) { g_lrm_norm_ranks = ranks; }

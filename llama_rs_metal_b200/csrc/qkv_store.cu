@@ -2,7 +2,8 @@
 // projections' biases, separates q, k and v, and writes k and v into the paged cache.
 //
 // The projection row is [q_heads * d | kv_heads * d | kv_heads * dv]: values may have another
-// width than queries and keys. `bias` (float32, the row's width, or null) is added in float32
+// width than queries and keys; dv = 0 is a projection without values (the values are the keys, or
+// live inside them), and nothing is written through the value pointers. `bias` (float32, the row's width, or null) is added in float32
 // before the result is rounded to the activation type. Cache layout: key pages
 // [page][kv_head][page_size][d], value pages [page][kv_head][page_size][dv]; dest_rows[t] =
 // page * page_size + row in page, or < 0 when the position is not kept (see rope_store.cu).
@@ -48,7 +49,7 @@ LRM_API int lrm_qkv_bias_store(const void* qkv, int dtype, const float* bias, vo
                                int tokens, int q_heads, int kv_heads, int d, int dv, int page_size,
                                cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (q_heads <= 0 || kv_heads < 0 || d <= 0 || dv <= 0 || page_size <= 0) return LRM_BAD_ARGUMENT;
+  if (q_heads <= 0 || kv_heads < 0 || d <= 0 || dv < 0 || page_size <= 0) return LRM_BAD_ARGUMENT;
   if (k_pages != nullptr && dest_rows == nullptr) return LRM_BAD_ARGUMENT;
   const int width = q_heads * d + kv_heads * (d + dv);
   const dim3 grid(tokens, (width + 1023) / 1024 > 0 ? (width + 1023) / 1024 : 1);

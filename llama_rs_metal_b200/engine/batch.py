@@ -59,6 +59,16 @@ class StepContext:
     longest_first: Optional[torch.Tensor] = None
     may_defer: bool = False
     next_folds_pending: bool = False
+    # The norm the next block applies first (when that block accepts its result from outside),
+    # and such a result: (norm, normalized activations of the stream as it stands). Whoever
+    # writes the stream last in a block may fill `normed`; the next block takes it or ignores it.
+    next_entry_norm: Any = None
+    normed: Any = None
+
+    def take_normed(self, norm):
+        """The stream's normalized activations if the block before left them for `norm`."""
+        kept, self.normed = self.normed, None
+        return kept[1] if kept is not None and kept[0] is norm else None
 
     def take_pending(self):
         """The pending partial sums (the caller adds them); none are pending afterwards."""

@@ -48,7 +48,7 @@ class DecoderModel:
             unknown = sorted(set(layer.parts) - set(parts))
             if unknown:
                 raise InvalidError(f"a {layer.block!r} layer has no role {', '.join(unknown)}")
-            self.blocks.append(block_class(**parts))
+            self.blocks.append(block_class(**parts, **layer.options))
             self._names.append({role: _full_names(layer.parts[role], part) for role, part in parts.items()})
         self.final_norm = build_part(NORMS, plan.final_norm, "norm")
         self._final_names = _full_names(plan.final_norm, self.final_norm)
@@ -160,6 +160,7 @@ class DecoderModel:
         # captured step, once before and once under capture) must compute it again from its arrays
         ctx.scratch.clear()
         ctx.fresh_kv.clear()
+        ctx.normed = None
         hidden = ops.embed_rows(self.embedding, ctx.token_ids, plan.embedding_scale)
         wanted = ctx.wanted_rows.numel() > 0
         schedule = plan.schedule
@@ -168,9 +169,14 @@ class DecoderModel:
             view = cache.view(entry.cache) if cache is not None else None
             # may this block's last product leave its K slices for the next reader of the stream?
             if i + 1 < len(schedule):
-                ctx.next_folds_pending = self.blocks[schedule[i + 1].layer].folds_pending_on_entry
+                following = self.blocks[schedule[i + 1].layer]
+                ctx.next_folds_pending = following.folds_pending_on_entry
+                # a block may hand the next one its stream already passed through that block's
+                # first norm (nothing may be added to the stream in between)
+                ctx.next_entry_norm = following.entry_norm if schedule[i + 1].add_offset is None else None
             else:
                 ctx.next_folds_pending = wanted and self.final_norm.folds_pending
+                ctx.next_entry_norm = None
             if entry.add_offset is not None:
                 hidden = ops.add_row_(hidden, self.stream_offsets[entry.add_offset])
             hidden = self.blocks[entry.layer].forward(hidden, ctx, view)

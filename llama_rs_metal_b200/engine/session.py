@@ -128,7 +128,7 @@ class Model:
             if hasattr(request, "parts"):  # several things kept by one mixer
                 return sum(need(part) for part in request.parts)
             if hasattr(request, "kv_heads"):
-                width = request.head_dim + (request.value_dim or request.head_dim)
+                width = request.head_dim + (0 if request.values_in_keys else request.value_dim or request.head_dim)
                 return pages * PAGE_SIZE * request.kv_heads * width * elem
             n = 1
             for s in request.shape:

@@ -18,6 +18,8 @@ from __future__ import annotations
 
 import ctypes
 import os
+from dataclasses import dataclass
+from typing import Optional
 
 import torch
 
@@ -32,6 +34,38 @@ force_cluster_size = None  # tests fix the CTAs per cluster of the fused decode 
 prefill_kernel = None  # tests pin the tcgen05 prompt kernel: "pingpong" or "single" (None: the rule in prefill())
 
 
+@dataclass(frozen=True)
+class Extras:
+    """What some attention layers have beyond the plain softmax over scaled scores.
+
+    sinks: float32 [query heads]; exp(sink_h) is added to the softmax's denominator (a key that
+        is always seen, has no value, and whose score is not scaled).
+    temperature: (coef, every); the query at position p counts 1 + coef * ln(floor((p + 1) / every)
+        + 1) times. The kernels put the factor into the score's scale, in float32.
+    """
+
+    sinks: Optional[torch.Tensor] = None
+    temperature: Optional[tuple] = None
+
+    @property
+    def plain(self) -> bool:
+        return self.sinks is None and self.temperature is None
+
+    def arguments(self):
+        """(sinks pointer, coef, every) as the kernels take them."""
+        coef, every = self.temperature if self.temperature is not None else (0.0, 0)
+        return _ptr(self.sinks), ctypes.c_float(coef), int(every)
+
+
+NO_EXTRAS = Extras()
+
+
+def _value_stride(kv) -> int:
+    """Elements between two value rows of a cache view: values that live inside the key rows are
+    read from the keys' storage with the keys' width."""
+    return kv.k.shape[3] if getattr(kv, "values_in_keys", False) else kv.v.shape[3]
+
+
 def _tiled(q, page_size: int) -> bool:
     return (not force_rowwise and q.dtype == torch.bfloat16
             and bool(library.load().lrm_attention_tiled_supports(q.shape[2], page_size)))
@@ -44,10 +78,29 @@ def _plain(q, dv: int, slopes, out_scale: float) -> bool:
 
 
 def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: float, window: int,
-            slopes=None, out_scale: float = 1.0) -> None:
+            slopes=None, out_scale: float = 1.0, extras=None, value_dim=None) -> None:
+    """`v` None: the values are the first `value_dim` columns of the key rows."""
     T, Hq, d = q.shape
-    dv = v.shape[2]
+    extras = extras or NO_EXTRAS
     lib = library.load()
+    if v is None or not extras.plain:
+        dv = value_dim if v is None else v.shape[2]
+        shared = v is None or v.data_ptr() == k.data_ptr()
+        if dv == d and _tiled(q, 64) and shared:
+            _done(lib.lrm_attention_prefill_tiled(_ptr(q), _ptr(k), _ptr(k), _ptr(out), _ptr(cu_seqlens),
+                                                  cu_seqlens.numel() - 1, max_seq_len, Hq, k.shape[1], d,
+                                                  ctypes.c_float(scale), window, _ptr(slopes),
+                                                  ctypes.c_float(out_scale), *extras.arguments(), _stream()),
+                  "attention_prefill_tiled")
+            return
+        _done(lib.lrm_attention_packed_rowwise(_ptr(q), _ptr(k), _ptr(k if v is None else v), _ptr(out),
+                                               _code(q.dtype), _ptr(cu_seqlens), _ptr(seq_of_token), T, Hq,
+                                               k.shape[1], d, dv, ctypes.c_float(scale), window, _ptr(slopes),
+                                               ctypes.c_float(out_scale), *extras.arguments(),
+                                               d if v is None else dv, _stream()),
+              "attention_packed_rowwise")
+        return
+    dv = v.shape[2]
     aligned = all(t.data_ptr() % 16 == 0 for t in (q, k, v, out))
     if (not force_rowwise and not force_warp_level and q.dtype == torch.bfloat16 and aligned
             and _plain(q, dv, slopes, out_scale) and lib.lrm_attention_prefill_umma_supports(d)):
@@ -84,13 +137,13 @@ def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: flo
         _done(lib.lrm_attention_prefill_tiled(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(cu_seqlens),
                                               cu_seqlens.numel() - 1, max_seq_len, Hq, k.shape[1], d,
                                               ctypes.c_float(scale), window, _ptr(slopes),
-                                              ctypes.c_float(out_scale), _stream()),
+                                              ctypes.c_float(out_scale), *NO_EXTRAS.arguments(), _stream()),
               "attention_prefill_tiled")
         return
     _done(lib.lrm_attention_packed_rowwise(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _code(q.dtype),
                                            _ptr(cu_seqlens), _ptr(seq_of_token), T, Hq, k.shape[1], d, dv,
                                            ctypes.c_float(scale), window, _ptr(slopes),
-                                           ctypes.c_float(out_scale), _stream()),
+                                           ctypes.c_float(out_scale), *NO_EXTRAS.arguments(), dv, _stream()),
           "attention_packed_rowwise")
 
 
@@ -106,9 +159,11 @@ def decode_splits(seqs: int, kv_heads: int, group: int, max_kv_len: int, window:
 
 
 def decode(q, kv, out, slots, kv_lens, max_kv_len: int, scale: float, window: int,
-           slopes=None, out_scale: float = 1.0) -> None:
+           slopes=None, out_scale: float = 1.0, extras=None) -> None:
+    from .ops import _value_dim
     B, Hq, d = q.shape
-    dv = kv.v.shape[3]
+    dv = _value_dim(kv)
+    extras = extras or NO_EXTRAS
     lib = library.load()
     if dv == d and _tiled(q, kv.page_size):
         splits = decode_splits(B, kv.kv_heads, Hq // kv.kv_heads, max_kv_len, window)
@@ -117,29 +172,33 @@ def decode(q, kv, out, slots, kv_lens, max_kv_len: int, scale: float, window: in
                                              _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
                                              _ptr(kv_lens), B, Hq, kv.kv_heads, d, kv.page_size,
                                              ctypes.c_float(scale), window, splits, _ptr(slopes),
-                                             ctypes.c_float(out_scale), _stream()),
+                                             ctypes.c_float(out_scale), *extras.arguments(), _stream()),
               "attention_decode_tiled", launches=2)
         return
     _done(lib.lrm_attention_paged_rowwise(_ptr(q), _ptr(kv.k), _ptr(kv.v), _ptr(out), _code(q.dtype),
                                           _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
                                           _ptr(kv_lens), None, None, B, Hq, kv.kv_heads, d, dv, kv.page_size,
                                           ctypes.c_float(scale), window, _ptr(slopes),
-                                          ctypes.c_float(out_scale), _stream()),
+                                          ctypes.c_float(out_scale), *extras.arguments(), _value_stride(kv),
+                                          _stream()),
           "attention_paged_rowwise")
 
 
 def extend(q, kv, out, cu_seqlens, seq_of_token, positions, slots, kv_lens, max_seq_len: int, scale: float,
-           window: int, slopes=None, out_scale: float = 1.0) -> None:
+           window: int, slopes=None, out_scale: float = 1.0, extras=None) -> None:
     """Packed queries, several per sequence, over the cache that already holds the step's keys."""
+    from .ops import _value_dim
     T, Hq, d = q.shape
-    dv = kv.v.shape[3]
+    dv = _value_dim(kv)
+    extras = extras or NO_EXTRAS
     lib = library.load()
     if dv == d and _tiled(q, kv.page_size):
         _done(lib.lrm_attention_extend_tiled(_ptr(q), _ptr(kv.k), _ptr(kv.v), _ptr(out), _ptr(cu_seqlens),
                                              _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
                                              _ptr(kv_lens), cu_seqlens.numel() - 1, max_seq_len, Hq,
                                              kv.kv_heads, d, kv.page_size, ctypes.c_float(scale), window,
-                                             _ptr(slopes), ctypes.c_float(out_scale), _stream()),
+                                             _ptr(slopes), ctypes.c_float(out_scale), *extras.arguments(),
+                                             _stream()),
               "attention_extend_tiled")
         return
     # the same arithmetic, key by key in ascending order, as the packed row-wise kernel: in
@@ -148,7 +207,8 @@ def extend(q, kv, out, cu_seqlens, seq_of_token, positions, slots, kv_lens, max_
                                           _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
                                           _ptr(kv_lens), _ptr(seq_of_token), _ptr(positions), T, Hq,
                                           kv.kv_heads, d, dv, kv.page_size, ctypes.c_float(scale), window,
-                                          _ptr(slopes), ctypes.c_float(out_scale), _stream()),
+                                          _ptr(slopes), ctypes.c_float(out_scale), *extras.arguments(),
+                                          _value_stride(kv), _stream()),
           "attention_paged_rowwise")
 
 
@@ -240,7 +300,7 @@ def decode_fused(qkv, positions, inv_freq, rotary: int, kv, dest_rows, out, slot
 # --------------------------------------------------------------------------- one call for a mixer
 def attend(projected, *, q_heads: int, kv_heads: int, head_dim: int, rotary, ctx, cache, writes_cache: bool,
            cache_entry: int, scale: float, window, projection=None, value_dim=None, bias=None, slopes=None,
-           out_scale: float = 1.0):
+           out_scale: float = 1.0, extras=None, values_are_keys: bool = False):
     """A layer's attention for one step: position rotation, cache write and attention, with the
     kernels chosen here for the step's phase, dtype and geometry. -> mixed heads [T, q_heads * d].
 
@@ -254,14 +314,18 @@ def attend(projected, *, q_heads: int, kv_heads: int, head_dim: int, rotary, ctx
         projection and the rotation: a prompt's product then rotates and stores in its epilogue.
     value_dim: head width of values when it is not head_dim; bias: float32 [projected width], added
         to the projection; slopes: float32 [q_heads], the linear distance penalty; out_scale: factor
-        on the result. With any of these the split kernel without rotation (csrc/qkv_store.cu) takes
-        the place of the rotation kernel, and attention runs on the kernels that know them.
+        on the result; extras: per-head sinks and a query temperature (Extras); values_are_keys:
+        the projection is q|k only and a key row is also its value row. With any of these the split
+        kernel without rotation (csrc/qkv_store.cu) takes the place of the rotation kernel, and
+        attention runs on the kernels that know them.
     """
     from . import ops
     inv_freq, width = rotary if rotary is not None else (None, 0)
     phase = ctx.phase
     dv = head_dim if value_dim is None else value_dim
-    if bias is not None or dv != head_dim or slopes is not None or out_scale != 1.0:
+    if values_are_keys:
+        dv = 0  # the projection has no value columns
+    if bias is not None or dv != head_dim or slopes is not None or out_scale != 1.0 or extras is not None:
         if inv_freq is not None:
             from ..errors import UnsupportedError
             raise UnsupportedError("attention with a bias, a distance penalty or values of another width "
@@ -275,15 +339,15 @@ def attend(projected, *, q_heads: int, kv_heads: int, head_dim: int, rotary, ctx
                                      keep_packed=prefill_phase and writes_cache)
         if prefill_phase:
             if writes_cache:
-                ctx.fresh_kv[cache_entry] = (k, v)
+                ctx.fresh_kv[cache_entry] = (k, k if values_are_keys else v)
             k, v = ctx.fresh_kv[cache_entry]
             return ops.attention_prefill(q, k, v, ctx.cu_seqlens, ctx.seq_of_token, ctx.max_seq_len, scale, window,
-                                         slopes, out_scale)
+                                         slopes, out_scale, extras)
         if phase == "decode":
             return ops.attention_decode(q, cache, ctx.slots, ctx.kv_lens, ctx.max_kv_len, scale, window, slopes,
-                                        out_scale)
+                                        out_scale, extras)
         return ops.attention_extend(q, cache, ctx.cu_seqlens, ctx.seq_of_token, ctx.positions, ctx.slots,
-                                    ctx.kv_lens, ctx.max_seq_len, scale, window, slopes, out_scale)
+                                    ctx.kv_lens, ctx.max_seq_len, scale, window, slopes, out_scale, extras)
     if projection is not None:
         x, weight = projection
         if (phase == "prefill" and writes_cache and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16

@@ -121,6 +121,32 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch
     return out
 
 
+def rms_norm_add_(stream: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, mult: float = 1.0,
+                  next_weight: Optional[torch.Tensor] = None, next_eps: Optional[float] = None,
+                  out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """stream += mult * RMSnorm(y) * weight, in place (stream and y float32 [T, h]: a norm behind a
+    sublayer). With `next_weight` (same dtype as `weight`) the updated rows are normalized again in the
+    same launch and returned as [T, h] in `out_dtype`: the norm in front of the next sublayer."""
+    _check(stream, "stream", torch.float32, 2)
+    _check(y, "y", torch.float32, 2)
+    _check(weight, "weight", dims=1)
+    T, hidden = stream.shape
+    if tuple(y.shape) != (T, hidden) or weight.numel() != hidden:
+        raise InvalidError("rms_norm_add_: y must match the stream, and the weight its rows")
+    out = None
+    if next_weight is not None:
+        _check(next_weight, "next_weight", weight.dtype, 1)
+        if next_weight.numel() != hidden or out_dtype is None:
+            raise InvalidError("rms_norm_add_: the second norm needs a weight per column and an output type")
+        out = _activation(T, hidden, out_dtype, stream.device)
+    _done(_lib().lrm_rms_norm_add(_ptr(stream), _ptr(y), _ptr(weight), _code(weight.dtype), ctypes.c_float(mult),
+                                  ctypes.c_float(eps), _ptr(next_weight), _ptr(out),
+                                  _code(out_dtype) if out is not None else F32,
+                                  ctypes.c_float(next_eps if next_eps is not None else eps), T, hidden, _stream()),
+          "rms_norm_add_")
+    return out
+
+
 # --------------------------------------------------------------------------- matrix products
 STORE, ADD, SILU_GATE = "store", "add", "silu_gate"
 
@@ -227,6 +253,22 @@ def silu_mul(gate_up: torch.Tensor, block: int) -> torch.Tensor:
     return out
 
 
+def clamped_gate_mul(gate_up: torch.Tensor, block: int, limit: float, alpha: float,
+                     out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), from [T, 2I]
+    whose columns alternate in blocks of `block` gate / up (float32, or the output's type)."""
+    _check(gate_up, "gate_up", dims=2)
+    inter = gate_up.shape[1] // 2
+    if gate_up.shape[1] % 2 or inter % block:
+        raise InvalidError("clamped_gate_mul: width must be 2*I with I a multiple of the block")
+    out_dtype = out_dtype or gate_up.dtype
+    out = _activation(gate_up.shape[0], inter, out_dtype, gate_up.device)
+    _done(_lib().lrm_clamped_gate_mul(_ptr(gate_up), _code(gate_up.dtype), _ptr(out), _code(out_dtype),
+                                      ctypes.c_longlong(gate_up.shape[0]), inter, block, ctypes.c_float(limit),
+                                      ctypes.c_float(alpha), _stream()), "clamped_gate_mul")
+    return out
+
+
 def add_(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     """x += delta, x float32 (the residual sum is always 32-bit)."""
     _check(x, "x", torch.float32)
@@ -326,7 +368,8 @@ def linear_rope_store(x: torch.Tensor, weight: torch.Tensor, q_heads: int, kv_he
 
 def qkv_bias_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_heads: int, kv_heads: int, head_dim: int,
                    value_dim: int, kv=None, dest_rows: Optional[torch.Tensor] = None, keep_packed: bool = True):
-    """Split a fused [T, Hq*d + Hk*d + Hk*dv] projection without rotation: add `bias` (float32, the
+    """Split a fused [T, Hq*d + Hk*d + Hk*dv] projection without rotation (value_dim 0: a projection
+    without values; v is then None and nothing is stored as values): add `bias` (float32, the
     row's width, or None), and return (q [T,Hq,d], k [T,Hk,d] or None, v [T,Hk,dv] or None); k and
     v are returned when `keep_packed`, and written to the paged cache view `kv` at `dest_rows`
     when given (see rope_store)."""
@@ -342,18 +385,19 @@ def qkv_bias_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_heads: int
     dev = qkv.device
     q = torch.empty((T, q_heads, head_dim), dtype=qkv.dtype, device=dev)
     k = torch.empty((T, kv_heads, head_dim), dtype=qkv.dtype, device=dev) if keep_packed else None
-    v = torch.empty((T, kv_heads, value_dim), dtype=qkv.dtype, device=dev) if keep_packed else None
+    v = torch.empty((T, kv_heads, value_dim), dtype=qkv.dtype, device=dev) if keep_packed and value_dim else None
     k_pages = v_pages = None
     page_size = 1
     if kv is not None and kv_heads > 0:
-        k_pages, v_pages, page_size = kv.k, kv.v, kv.page_size
+        k_pages, v_pages, page_size = kv.k, kv.v if value_dim else None, kv.page_size
         _check(k_pages, "k pages", qkv.dtype, 4)
-        _check(v_pages, "v pages", qkv.dtype, 4)
+        if value_dim:
+            _check(v_pages, "v pages", qkv.dtype, 4)
         _check(dest_rows, "dest_rows", torch.int32, 1)
         if dest_rows.numel() != T:
             raise InvalidError("qkv_bias_store: one destination row per token")
         if (tuple(k_pages.shape[1:]) != (kv_heads, page_size, head_dim)
-                or tuple(v_pages.shape[1:]) != (kv_heads, page_size, value_dim)):
+                or (value_dim and tuple(v_pages.shape[1:]) != (kv_heads, page_size, value_dim))):
             raise InvalidError("qkv_bias_store: cache pages do not match the head geometry")
     _done(_lib().lrm_qkv_bias_store(_ptr(qkv), _code(qkv.dtype), _ptr(bias), _ptr(q), _ptr(k), _ptr(v),
                                     _ptr(k_pages), _ptr(v_pages), _ptr(dest_rows if k_pages is not None else None),
@@ -464,6 +508,170 @@ def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: 
                                        _ptr(out), _ptr(cu_seqlens), _ptr(slots), slots.numel(), H, KH, d, dv,
                                        _stream()), "linear_state_scan")
     return out
+
+
+def short_conv(src: torch.Tensor, column: int, channels: int, in_bias: Optional[torch.Tensor], taps: torch.Tensor,
+               conv_bias: Optional[torch.Tensor], tails: torch.Tensor, cu_seqlens: torch.Tensor,
+               seq_of_token: torch.Tensor, slots: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """A causal convolution per channel over the columns column .. column + channels of src [T, W]
+    (+ in_bias, float32 [channels]): taps float32 [channels, n], the last tap on the current token,
+    zeros before a sequence's start; + conv_bias. Inputs before the step come from, and the step's
+    last n - 1 inputs go to, `tails` float32 [slots, n - 1, channels]. -> [T, channels] in out_dtype."""
+    _check(src, "src", dims=2)
+    _check(taps, "taps", torch.float32, 2)
+    T = src.shape[0]
+    n = taps.shape[1]
+    for name, t in (("cu_seqlens", cu_seqlens), ("seq_of_token", seq_of_token), ("slots", slots)):
+        _check(t, name, torch.int32, 1)
+    for name, t in (("in_bias", in_bias), ("conv_bias", conv_bias)):
+        if t is not None:
+            _check(t, name, torch.float32, 1)
+            if t.numel() != channels:
+                raise InvalidError(f"short_conv: {name} must have one entry per channel")
+    if n > 1:
+        _check(tails, "tails", torch.float32, 3)
+    if taps.shape[0] != channels or column + channels > src.shape[1] or \
+            (n > 1 and tuple(tails.shape[1:]) != (n - 1, channels)):
+        raise InvalidError("short_conv: shapes do not agree")
+    out = _activation(T, channels, out_dtype, src.device)
+    _done(_lib().lrm_short_conv(_ptr(src), _code(src.dtype), ctypes.c_longlong(src.shape[1]), column, _ptr(in_bias),
+                                _ptr(taps), _ptr(conv_bias), n, _ptr(tails) if n > 1 else ctypes.c_void_p(0),
+                                _ptr(cu_seqlens), _ptr(seq_of_token), _ptr(slots), _ptr(out), _code(out_dtype), T,
+                                slots.numel(), channels, _stream()), "short_conv", launches=2 if n > 1 else 1)
+    return out
+
+
+def gated_linear_scan(u: torch.Tensor, gates: torch.Tensor, y: torch.Tensor, y_column: int,
+                      y_bias: Optional[torch.Tensor], rate: torch.Tensor, state: torch.Tensor,
+                      cu_seqlens: torch.Tensor, slots: torch.Tensor, longest: int, blocks: int) -> torch.Tensor:
+    """S <- a S + sqrt(1 - a^2) (i u) per channel with a = exp(-rate sigmoid(gr)), i = sigmoid(gi); the
+    result is S gelu_tanh(y + y_bias). u [T, C] (activation type); gates float32 [T, 2C], per block of
+    C / blocks channels its gr then its gi; y: columns y_column .. of a float32 [T, W] activation;
+    rate float32 [C]; state float32 [slots, C], updated in place. `longest`: most tokens of one
+    sequence in the step (launch geometry only). -> [T, C] in u's type."""
+    _check(u, "u", dims=2)
+    T, C = u.shape
+    _check(gates, "gates", torch.float32, 2)
+    _check(y, "y", torch.float32, 2)
+    _check(rate, "rate", torch.float32, 1)
+    _check(state, "state", torch.float32, 2)
+    _check(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    _check(slots, "slots", torch.int32, 1)
+    if y_bias is not None:
+        _check(y_bias, "y_bias", torch.float32, 1)
+    if (tuple(gates.shape) != (T, 2 * C) or y.shape[0] != T or y_column + C > y.shape[1] or rate.numel() != C
+            or state.shape[1] != C or C % blocks or (y_bias is not None and y_bias.numel() != C)):
+        raise InvalidError("gated_linear_scan: shapes do not agree")
+    out = _activation(T, C, u.dtype, u.device)
+    _done(_lib().lrm_gated_linear_scan(_ptr(u), _code(u.dtype), _ptr(gates), _ptr(y), ctypes.c_longlong(y.shape[1]),
+                                       y_column, _ptr(y_bias), _ptr(rate), _ptr(state), _ptr(out), _ptr(cu_seqlens),
+                                       _ptr(slots), slots.numel(), longest, C, blocks, _stream()),
+          "gated_linear_scan")
+    return out
+
+
+def blockwise_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                     row_scale: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+                     x_column: int = 0, x_block: Optional[int] = None, out: Optional[torch.Tensor] = None,
+                     out_column: int = 0, out_block: Optional[int] = None) -> torch.Tensor:
+    """out[t, b, :] = (weight[b] . x[t, b, :] + bias[b]) * row_scale[t, b] with weight [B, n, m] ([out,
+    in] per block), bias float32 [B, n], row_scale float32 [T, B]. Block b of row t of x [T, W] starts
+    at column x_column + b * x_block (default: m, blocks side by side); the result goes to a new
+    [T, B * n] tensor in out_dtype, or into `out` [T, W'] at column out_column + b * out_block."""
+    _check(x, "x", dims=2)
+    _check(weight, "weight", dims=3)
+    T = x.shape[0]
+    B, n, m = weight.shape
+    x_block = m if x_block is None else x_block
+    if x_column + (B - 1) * x_block + m > x.shape[1]:
+        raise InvalidError("blockwise_linear: blocks outside the input row")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 2)
+        if tuple(bias.shape) != (B, n):
+            raise InvalidError("blockwise_linear: bias must be [blocks, out]")
+    if row_scale is not None:
+        _check(row_scale, "row_scale", torch.float32, 2)
+        if tuple(row_scale.shape) != (T, B):
+            raise InvalidError("blockwise_linear: row_scale must be [T, blocks]")
+    if out is None:
+        out = _activation(T, B * n, out_dtype or x.dtype, x.device)
+        out_column, out_block = 0, n
+    else:
+        _check(out, "out", dims=2)
+        out_block = n if out_block is None else out_block
+        if out.shape[0] != T or out_column + (B - 1) * out_block + n > out.shape[1]:
+            raise InvalidError("blockwise_linear: blocks outside the output row")
+    _done(_lib().lrm_blockwise_linear(_column_ptr(x, x_column), _code(x.dtype), ctypes.c_longlong(x.shape[1]),
+                                      ctypes.c_longlong(x_block), _ptr(weight), _code(weight.dtype), _ptr(bias),
+                                      _ptr(row_scale), _column_ptr(out, out_column), _code(out.dtype),
+                                      ctypes.c_longlong(out.shape[1]), ctypes.c_longlong(out_block), T, B, n, m,
+                                      _stream()), "blockwise_linear")
+    return out
+
+
+def rope_heads(src: torch.Tensor, src_column: int, src_head: int, dst: torch.Tensor, dst_column: int, dst_head: int,
+               positions: torch.Tensor, inv_freq: torch.Tensor, heads: int) -> torch.Tensor:
+    """For every token and head: the 2 * len(inv_freq) columns of src [T, W] at src_column + h * src_head,
+    rotated by position (pairs i, i + half, angle = float(position) * inv_freq[i]), written to dst
+    [T, W'] at dst_column + h * dst_head."""
+    _check(src, "src", dims=2)
+    _check(dst, "dst", src.dtype, 2)
+    _check(positions, "positions", torch.int32, 1)
+    _check(inv_freq, "inv_freq", torch.float32, 1)
+    T, rot = src.shape[0], 2 * inv_freq.numel()
+    if (dst.shape[0] != T or positions.numel() != T or src_column + (heads - 1) * src_head + rot > src.shape[1]
+            or dst_column + (heads - 1) * dst_head + rot > dst.shape[1]):
+        raise InvalidError("rope_heads: columns outside a row")
+    _done(_lib().lrm_rope_heads(_column_ptr(src, src_column), _code(src.dtype), ctypes.c_longlong(src.shape[1]),
+                                ctypes.c_longlong(src_head), _column_ptr(dst, dst_column),
+                                ctypes.c_longlong(dst.shape[1]), ctypes.c_longlong(dst_head), _ptr(positions),
+                                _ptr(inv_freq), rot, T, heads, _stream()), "rope_heads")
+    return dst
+
+
+def latent_prepare(proj: torch.Tensor, q_column: int, q_weight: torch.Tensor, c_column: int,
+                   c_weight: Optional[torch.Tensor], rot: int, positions: torch.Tensor,
+                   inv_freq: Optional[torch.Tensor], eps: float, gate_column: int, heads: int,
+                   out_dtype: torch.dtype, kv=None, dest_rows: Optional[torch.Tensor] = None,
+                   keep_packed: bool = True):
+    """From a fused down-projection [T, W]: the normed query latent [T, q_rank] (out_dtype), the gates
+    sigmoid(.) float32 [T, heads], and, when the row has key/value columns (c_column >= 0), the rows
+    [RMSnorm(latent) * c_weight | rotated shared key part] [T, kv_rank + rot], returned when
+    `keep_packed` and written into the paged cache view `kv` (one key head of that width) at
+    `dest_rows`. Norm weights float32. -> (cq, rows or None, gate)."""
+    _check(proj, "proj", dims=2)
+    _check(q_weight, "q_weight", torch.float32, 1)
+    _check(positions, "positions", torch.int32, 1)
+    T, q_rank = proj.shape[0], q_weight.numel()
+    kv_rank = 0
+    if c_column >= 0:
+        _check(c_weight, "c_weight", torch.float32, 1)
+        kv_rank = c_weight.numel()
+        if rot:
+            _check(inv_freq, "inv_freq", torch.float32, 1)
+            if inv_freq.numel() * 2 != rot:
+                raise InvalidError("latent_prepare: inv_freq must have rot/2 entries")
+        if c_column + kv_rank + rot > proj.shape[1]:
+            raise InvalidError("latent_prepare: key/value columns outside the projection")
+    if q_column + q_rank > proj.shape[1] or gate_column + heads > proj.shape[1]:
+        raise InvalidError("latent_prepare: columns outside the projection")
+    cq = _activation(T, q_rank, out_dtype, proj.device)
+    gate = _f32((T, heads), proj.device)
+    rows, pages, dest = None, None, None
+    if c_column >= 0:
+        if keep_packed:
+            rows = torch.empty((T, kv_rank + rot), dtype=out_dtype, device=proj.device)
+        if kv is not None:
+            pages, dest = kv.k, dest_rows
+            _check(pages, "k pages", out_dtype, 4)
+            _check(dest, "dest_rows", torch.int32, 1)
+            if pages.shape[1] != 1 or pages.shape[3] != kv_rank + rot or dest.numel() != T:
+                raise InvalidError("latent_prepare: the cache keeps one key head of width kv_rank + rot")
+    _done(_lib().lrm_latent_prepare(_ptr(proj), _code(proj.dtype), ctypes.c_longlong(proj.shape[1]), q_column, q_rank,
+                                    _ptr(q_weight), c_column, kv_rank, _ptr(c_weight), rot, _ptr(positions),
+                                    _ptr(inv_freq), ctypes.c_float(eps), _ptr(cq), _ptr(rows), _ptr(pages), _ptr(dest),
+                                    gate_column, heads, _ptr(gate), _code(out_dtype), T, _stream()), "latent_prepare")
+    return cq, rows, gate
 
 
 GATE_SILU, GATE_SIGMOID = 1, 2
@@ -601,15 +809,37 @@ def _check_slopes(slopes: Optional[torch.Tensor], heads: int) -> None:
             raise InvalidError("one distance slope per query head")
 
 
-def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor,
+def _check_extras(extras, heads: int) -> None:
+    if extras is not None and extras.sinks is not None:
+        _check(extras.sinks, "sinks", torch.float32, 1)
+        if extras.sinks.numel() != heads:
+            raise InvalidError("one sink per query head")
+
+
+def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: Optional[torch.Tensor], cu_seqlens: torch.Tensor,
                       seq_of_token: torch.Tensor, max_seq_len: int, scale: float,
                       window: Optional[int] = None, slopes: Optional[torch.Tensor] = None,
-                      out_scale: float = 1.0) -> torch.Tensor:
+                      out_scale: float = 1.0, extras=None, value_dim: Optional[int] = None) -> torch.Tensor:
     """Causal GQA over the step's own packed k, v (sequences start at position 0). -> [T, Hq*dv]
     (v may have another head width dv than q and k). `slopes` (float32 [Hq]): a key n positions
-    behind the query loses slopes[h] * n from its score. `out_scale` multiplies the result."""
+    behind the query loses slopes[h] * n from its score. `out_scale` multiplies the result.
+    v None: the values are the first `value_dim` columns (default: all) of the key rows.
+    `extras` (attention_dispatch.Extras): per-head sinks, a query temperature."""
     _check(q, "q", dims=3)
     _check(k, "k", q.dtype, 3)
+    _check_extras(extras, q.shape[1])
+    if v is None:
+        dv = k.shape[2] if value_dim is None else value_dim
+        if not 0 < dv <= k.shape[2] or q.shape[1] % k.shape[1] or k.shape[0] != q.shape[0] or k.shape[2] != q.shape[2]:
+            raise InvalidError("attention_prefill: q and k shapes do not agree")
+        _check(cu_seqlens, "cu_seqlens", torch.int32, 1)
+        _check(seq_of_token, "seq_of_token", torch.int32, 1)
+        _check_slopes(slopes, q.shape[1])
+        out = _activation(q.shape[0], q.shape[1] * dv, q.dtype, q.device)
+        from . import attention_dispatch
+        attention_dispatch.prefill(q, k, None, out, cu_seqlens, seq_of_token, max_seq_len, scale, window or 0,
+                                   slopes, out_scale, extras, dv)
+        return out
     _check(v, "v", q.dtype, 3)
     _check(cu_seqlens, "cu_seqlens", torch.int32, 1)
     _check(seq_of_token, "seq_of_token", torch.int32, 1)
@@ -621,18 +851,20 @@ def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seql
     out = _activation(T, Hq * v.shape[2], q.dtype, q.device)
     from . import attention_dispatch
     attention_dispatch.prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len, scale, window or 0,
-                               slopes, out_scale)
+                               slopes, out_scale, extras)
     return out
 
 
 def _value_dim(kv) -> int:
-    return kv.v.shape[3]
+    """Head width of a cache view's values (which may be the first columns of its key rows)."""
+    return kv.value_dim if getattr(kv, "value_dim", None) else kv.v.shape[3]
 
 
 def attention_decode(q: torch.Tensor, kv, slots: torch.Tensor, kv_lens: torch.Tensor,
                      max_kv_len: int, scale: float, window: Optional[int] = None,
-                     slopes: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> torch.Tensor:
+                     slopes: Optional[torch.Tensor] = None, out_scale: float = 1.0, extras=None) -> torch.Tensor:
     """One query per sequence over its cached keys (the newest already stored). -> [B, Hq*dv]"""
+    _check_extras(extras, q.shape[1])
     _check(q, "q", dims=3)
     _check(kv.k, "k pages", q.dtype, 4)
     _check(kv.v, "v pages", q.dtype, 4)
@@ -645,14 +877,14 @@ def attention_decode(q: torch.Tensor, kv, slots: torch.Tensor, kv_lens: torch.Te
     _check_slopes(slopes, Hq)
     out = _activation(B, Hq * _value_dim(kv), q.dtype, q.device)
     from . import attention_dispatch
-    attention_dispatch.decode(q, kv, out, slots, kv_lens, max_kv_len, scale, window or 0, slopes, out_scale)
+    attention_dispatch.decode(q, kv, out, slots, kv_lens, max_kv_len, scale, window or 0, slopes, out_scale, extras)
     return out
 
 
 def attention_extend(q: torch.Tensor, kv, cu_seqlens: torch.Tensor, seq_of_token: torch.Tensor,
                      positions: torch.Tensor, slots: torch.Tensor, kv_lens: torch.Tensor, max_seq_len: int,
                      scale: float, window: Optional[int] = None, slopes: Optional[torch.Tensor] = None,
-                     out_scale: float = 1.0) -> torch.Tensor:
+                     out_scale: float = 1.0, extras=None) -> torch.Tensor:
     """Several queries per sequence over the cache, which already holds the step's own keys:
     query t (packed, of sequence seq_of_token[t]) sees the keys up to positions[t]. -> [T, Hq*d]"""
     _check(q, "q", dims=3)
@@ -671,8 +903,9 @@ def attention_extend(q: torch.Tensor, kv, cu_seqlens: torch.Tensor, seq_of_token
     _check_slopes(slopes, Hq)
     out = _activation(T, Hq * _value_dim(kv), q.dtype, q.device)
     from . import attention_dispatch
+    _check_extras(extras, Hq)
     attention_dispatch.extend(q, kv, out, cu_seqlens, seq_of_token, positions, slots, kv_lens, max_seq_len,
-                              scale, window or 0, slopes, out_scale)
+                              scale, window or 0, slopes, out_scale, extras)
     return out
 
 

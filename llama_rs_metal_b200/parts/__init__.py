@@ -5,12 +5,15 @@ from .norm import RMSNorm
 from .rope import DistancePenalty, RotaryEmbedding
 from .attention import Attention
 from .mlp import GatedMLP
-from .recurrent import GatedDeltaRule, Retention
+from .recurrent import GatedDeltaRule, GatedLinearRecurrence, Retention
+from .latent import LatentAttention
 from .parallel import ParallelMixer
 from .moe import MixtureOfExperts
-from .block import PreNormBlock, PreNormMixerBlock
+from .block import PreNormBlock, PreNormMixerBlock, SandwichNormBlock, SandwichNormMixerBlock
 
 __all__ = ["Block", "CompositeRequest", "FeedForward", "KeyValueRequest", "LayerSpec", "Mixer", "ModelPlan", "Norm",
            "Part", "PartSpec", "PositionEncoding", "ScheduleEntry", "StateRequest", "LinearWeight",
            "RMSNorm", "RotaryEmbedding", "DistancePenalty", "Attention", "GatedMLP", "Retention", "GatedDeltaRule",
-           "ParallelMixer", "MixtureOfExperts", "PreNormBlock", "PreNormMixerBlock"]
+           "GatedLinearRecurrence", "LatentAttention",
+           "ParallelMixer", "MixtureOfExperts", "PreNormBlock", "PreNormMixerBlock", "SandwichNormBlock",
+           "SandwichNormMixerBlock"]

@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 import math
-from typing import Dict, Optional
+from typing import Dict, Optional, Sequence
 
 import torch
 
@@ -31,14 +31,29 @@ class Attention(Mixer):
     `output_scale`, a factor on the mixer's output (a mixer that enters a weighted sum of
     mixers), applied to the mixed heads before the output projection. A position scheme that
     is a linear distance penalty (`distance_slopes`) is applied by the attention kernels.
+    `values_are_keys`: there is no value projection, a token's key row is its value row too, and
+    the cache keeps keys only; `sinks`: a learned number per query head (tensor `sinks`) whose
+    exponential joins the softmax's denominator; `query_temperature` (coef, every): the query
+    at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).
     """
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: Optional[PartSpec] = None, window: Optional[int] = None,
                  scale: Optional[float] = None, value_dim: Optional[int] = None, bias: bool = False,
-                 output_scale: float = 1.0):
+                 output_scale: float = 1.0, values_are_keys: bool = False, sinks: bool = False,
+                 query_temperature: Optional[Sequence[float]] = None):
         if num_heads <= 0 or num_kv_heads <= 0 or num_heads % num_kv_heads:
             raise InvalidError("attention heads must be a multiple of key/value heads")
+        self.values_are_keys, self.has_sinks = bool(values_are_keys), bool(sinks)
+        if self.values_are_keys and value_dim not in (None, head_dim):
+            raise InvalidError("values that are the keys have the keys' width")
+        self.query_temperature = None
+        if query_temperature is not None:
+            coef, every = float(query_temperature[0]), int(query_temperature[1])
+            if every <= 0:
+                raise InvalidError("a query temperature grows every so many positions: a positive number")
+            self.query_temperature = (coef, every)
+        self.extras = None
         self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
         self.head_dim, self.window = head_dim, window
         self.value_dim = head_dim if value_dim is None else int(value_dim)
@@ -60,9 +75,14 @@ class Attention(Mixer):
         v, mixed = self.num_kv_heads * self.value_dim, self.num_heads * self.value_dim
         out = {"q_proj.weight": TensorSpec((q, h)), "k_proj.weight": TensorSpec((kv, h)),
                "v_proj.weight": TensorSpec((v, h)), "o_proj.weight": TensorSpec((h, mixed))}
+        if self.values_are_keys:
+            del out["v_proj.weight"]
+        if self.has_sinks:
+            out["sinks"] = TensorSpec((self.num_heads,))
         if self.has_bias:
-            out.update({"q_proj.bias": TensorSpec((q,)), "k_proj.bias": TensorSpec((kv,)),
-                        "v_proj.bias": TensorSpec((v,))})
+            out.update({"q_proj.bias": TensorSpec((q,)), "k_proj.bias": TensorSpec((kv,))})
+            if not self.values_are_keys:
+                out["v_proj.bias"] = TensorSpec((v,))
         if self.position is not None:
             out.update({"position." + n: s for n, s in self.position.tensors().items()})
         return out
@@ -78,29 +98,36 @@ class Attention(Mixer):
             index = torch.tensor(order, dtype=torch.long, device=q_weight.device)
             q_weight = q_weight.view(self.num_heads, self.head_dim, -1)[:, index].reshape(q_weight.shape)
             k_weight = k_weight.view(self.num_kv_heads, self.head_dim, -1)[:, index].reshape(k_weight.shape)
-        fused = torch.cat([q_weight, k_weight, weights["v_proj.weight"]], dim=0).contiguous()
+        rows = [q_weight, k_weight] if self.values_are_keys else [q_weight, k_weight, weights["v_proj.weight"]]
+        fused = torch.cat(rows, dim=0).contiguous()
+        if self.has_sinks or self.query_temperature is not None:
+            from ..kernels.attention_dispatch import Extras
+            sinks = weights["sinks"].to(torch.float32).contiguous() if self.has_sinks else None
+            self.extras = Extras(sinks, self.query_temperature)
         self.qkv = LinearWeight(fused)
         self.q_only = LinearWeight(fused[: self.num_heads * self.head_dim])
         self.out = LinearWeight(weights["o_proj.weight"])
         if self.has_bias:
             if order is not None:
                 raise InvalidError("projection biases with a reordered head are not built")
-            self.bias = torch.cat([weights["q_proj.bias"], weights["k_proj.bias"], weights["v_proj.bias"]]) \
-                .to(torch.float32).contiguous()
+            biases = ["q_proj.bias", "k_proj.bias"] + ([] if self.values_are_keys else ["v_proj.bias"])
+            self.bias = torch.cat([weights[n] for n in biases]).to(torch.float32).contiguous()
         if self.position is not None:
             self.position.bind({n[len("position."):]: t for n, t in weights.items()
                                 if n.startswith("position.")}, runtime)
 
     def cache_request(self):
         return KeyValueRequest(self.num_kv_heads, self.head_dim, self.window,
-                               None if self.value_dim == self.head_dim else self.value_dim)
+                               None if self.value_dim == self.head_dim else self.value_dim,
+                               values_in_keys=self.values_are_keys)
 
     def forward(self, x, ctx, cache, residual):
         entry = ctx.entry
         weight = self.qkv if entry.writes_cache else self.q_only
         rotary = self.position.rotary_table() if self.position is not None else None
         slopes = self.position.distance_slopes() if self.position is not None else None
-        if self.has_bias or self.value_dim != self.head_dim or slopes is not None or self.output_scale != 1.0:
+        if (self.has_bias or self.value_dim != self.head_dim or slopes is not None or self.output_scale != 1.0
+                or self.values_are_keys or self.extras is not None):
             # the general form: projection, then a split that adds the biases and stores keys and
             # values, then the attention kernels that know the penalty and the value width
             bias = self.bias
@@ -110,7 +137,8 @@ class Attention(Mixer):
                                head_dim=self.head_dim, rotary=rotary, ctx=ctx, cache=cache,
                                writes_cache=entry.writes_cache, cache_entry=entry.cache, scale=self.scale,
                                window=self.window, value_dim=self.value_dim, bias=bias, slopes=slopes,
-                               out_scale=self.output_scale)
+                               out_scale=self.output_scale, extras=self.extras,
+                               values_are_keys=self.values_are_keys)
             return self.out(mixed, epilogue=ops.ADD, out=residual, ctx=ctx)
         # Nothing stands between projection and rotation unless a variant mixer overrides the hook
         # or the position scheme is no rotary table: the kernels may then do both in one launch.

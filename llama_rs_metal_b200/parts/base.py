@@ -40,17 +40,20 @@ class LayerSpec:
     can be given by name; any other set goes in `parts`.
     """
 
-    __slots__ = ("block", "parts")
+    __slots__ = ("block", "parts", "options")
 
     def __init__(self, block: str, mixer: Optional[PartSpec] = None, feed_forward: Optional[PartSpec] = None,
                  mixer_norm: Optional[PartSpec] = None, feed_forward_norm: Optional[PartSpec] = None,
-                 parts: Optional[Mapping[str, PartSpec]] = None):
+                 parts: Optional[Mapping[str, PartSpec]] = None, options: Optional[Mapping[str, Any]] = None):
         named = {"mixer": mixer, "feed_forward": feed_forward, "mixer_norm": mixer_norm,
                  "feed_forward_norm": feed_forward_norm}
         merged = {role: spec for role, spec in named.items() if spec is not None}
         merged.update(parts or {})
         object.__setattr__(self, "block", block)
         object.__setattr__(self, "parts", merged)
+        # constants of the arrangement itself (a factor on what a sublayer adds), passed to the
+        # block's constructor by keyword beside its parts
+        object.__setattr__(self, "options", dict(options or {}))
 
     def __setattr__(self, name, value):
         raise AttributeError("LayerSpec is immutable; use with_parts()")
@@ -64,7 +67,7 @@ class LayerSpec:
 
     def with_parts(self, **changes: PartSpec) -> "LayerSpec":
         """A copy with some roles' parts replaced or added."""
-        return LayerSpec(self.block, parts={**self.parts, **changes})
+        return LayerSpec(self.block, parts={**self.parts, **changes}, options=self.options)
 
     def __repr__(self):
         return f"LayerSpec({self.block!r}, {dict(self.parts)!r})"
@@ -112,14 +115,17 @@ class KeyValueRequest:
     """A mixer whose memory grows with the sequence: keys and values per token.
 
     `window` None keeps every key; a number keeps the last `window` positions.
-    `value_dim` None: values are as wide as keys. Layers with equal requests share
-    one storage group.
+    `value_dim` None: values are as wide as keys. `values_in_keys`: a token's value row is the
+    first `value_dim` columns of its key row (all of it when `value_dim` is None), so only keys
+    are stored and the attention kernels read values out of them. Layers with equal requests
+    share one storage group.
     """
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
     value_dim: Optional[int] = None
+    values_in_keys: bool = False
 
 
 @dataclass(frozen=True)
@@ -167,6 +173,13 @@ class Norm(Part):
         """float32 residual [T,h] -> normalized activations [T,h] (or [len(rows),h])."""
         raise NotImplementedError
 
+    def add_into(self, hidden: torch.Tensor, y: torch.Tensor, ctx, mult: float = 1.0,
+                 then: Optional["Norm"] = None) -> Optional[torch.Tensor]:
+        """hidden += mult * norm(y) for a sublayer's float32 output y [T,h] (a norm behind the
+        sublayer). With `then`, also returns then.forward(hidden) of the updated stream, which a
+        norm may compute in the same pass."""
+        raise NotImplementedError
+
 
 class PositionEncoding(Part):
     def rotary_table(self) -> Optional[Tuple[torch.Tensor, int]]:
@@ -198,18 +211,21 @@ class Mixer(Part):
         """KeyValueRequest, StateRequest, CompositeRequest or None."""
         return None
 
-    def forward(self, x: torch.Tensor, ctx, cache, residual: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx, cache, residual: Optional[torch.Tensor]) -> torch.Tensor:
         """x: normalized activations [T,h]. Returns the new residual stream.
 
         `residual` is the float32 stream the mixer's output is added to; the
         part may add in place (a fused epilogue) and return the same tensor.
+        With `residual` None (a block that puts something between the part and the
+        stream, a norm for instance) the part returns its own output, float32 [T,h].
         `cache` is the view of this schedule entry's cache storage (or None).
         """
         raise NotImplementedError
 
 
 class FeedForward(Part):
-    def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx, residual: Optional[torch.Tensor]) -> torch.Tensor:
+        """As Mixer.forward: added into `residual`, or returned as float32 when it is None."""
         raise NotImplementedError
 
 
@@ -221,6 +237,10 @@ class Block(Part):
 
     roles: Mapping[str, str] = {"mixer": "mixer", "feed_forward": "feed_forward",
                                 "mixer_norm": "norm", "feed_forward_norm": "norm"}
+
+    # the norm a block applies first to the stream it is given, when the block accepts that
+    # norm's result from whoever wrote the stream last (StepContext.normed); None otherwise
+    entry_norm: Optional[Norm] = None
 
     def __init__(self, **parts: Part):
         missing = [role for role in self.roles if role not in parts]

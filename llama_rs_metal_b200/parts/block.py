@@ -49,3 +49,56 @@ class PreNormMixerBlock(Block):
         hidden = self.mixer.forward(x, ctx, cache, residual=hidden)
         ctx.may_defer = False
         return hidden
+
+
+class _SandwichBlock(Block):
+    """Norms on both sides of every sublayer, and a factor on what a sublayer adds:
+    hidden += mult * post_norm(sublayer(pre_norm(hidden))). The sublayer's output stays float32
+    up to its norm. The post-norm's pass also applies the norm that comes next (the
+    feed-forward's pre-norm, or the next block's first norm when that block takes it)."""
+
+    graph_safe = True
+
+    def __init__(self, residual_mult: float = 1.0, **parts):
+        super().__init__(**parts)
+        self.residual_mult = float(residual_mult)
+
+    @property
+    def entry_norm(self):
+        return self.mixer_norm
+
+    def _mixer_half(self, hidden, ctx, cache, then):
+        x = ctx.take_normed(self.mixer_norm)
+        if x is None:
+            x = self.mixer_norm.forward(hidden, ctx)
+        y = self.mixer.forward(x, ctx, cache, residual=None)
+        return self.mixer_post_norm.add_into(hidden, y, ctx, self.residual_mult, then)
+
+
+@register_block("sandwich_norm")
+class SandwichNormBlock(_SandwichBlock):
+    """A mixer and a feed-forward, each between two norms."""
+
+    roles = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "mixer_post_norm": "norm",
+             "feed_forward_norm": "norm", "feed_forward_post_norm": "norm"}
+
+    def forward(self, hidden, ctx, cache):
+        following = ctx.next_entry_norm
+        x = self._mixer_half(hidden, ctx, cache, self.feed_forward_norm)
+        y = self.feed_forward.forward(x, ctx, residual=None)
+        normed = self.feed_forward_post_norm.add_into(hidden, y, ctx, self.residual_mult, following)
+        ctx.normed = (following, normed) if following is not None else None
+        return hidden
+
+
+@register_block("sandwich_norm_mixer")
+class SandwichNormMixerBlock(_SandwichBlock):
+    """A mixer between two norms: a layer without a feed-forward."""
+
+    roles = {"mixer": "mixer", "mixer_norm": "norm", "mixer_post_norm": "norm"}
+
+    def forward(self, hidden, ctx, cache):
+        following = ctx.next_entry_norm
+        normed = self._mixer_half(hidden, ctx, cache, following)
+        ctx.normed = (following, normed) if following is not None else None
+        return hidden

@@ -43,8 +43,12 @@ class LinearWeight:
                  out_dtype: Optional[torch.dtype] = None, ctx=None) -> torch.Tensor:
         """`ctx` (a StepContext) may be given with epilogue "add" for a part's last addition into
         the residual stream: while ctx.may_defer is set, a product that is cut into K slices
-        leaves them in ctx.pending for the next norm to add instead of adding them here."""
+        leaves them in ctx.pending for the next norm to add instead of adding them here. Epilogue
+        "add" with `out` None (a block that puts a norm between a part and the stream) returns
+        the product itself, in float32."""
         w = self.weight
+        if epilogue == ops.ADD and out is None:
+            epilogue, out_dtype, ctx = ops.STORE, torch.float32, None
         if x.dtype == w.dtype:
             if epilogue == ops.ADD and ctx is not None and ctx.may_defer:
                 planes = ops.linear_slices(x, w)

@@ -18,14 +18,18 @@ GATE_BLOCK = 8  # rows of gate and up alternate in blocks of this many in the fu
 @register_feed_forward("gated_mlp")
 class GatedMLP(FeedForward):
     """down( act(x Wg^T) * (x Wu^T) ), added to the residual stream
-    (crates/model-runtime/src/execute.rs:251-267). Only SiLU is built, as in the
-    reference (crates/model-format/src/mlx/config.rs:58-64)."""
+    (crates/model-runtime/src/execute.rs:251-267). The reference builds SiLU only
+    (crates/model-format/src/mlx/config.rs:58-64). Activation "clamped_gate" is the gate of the
+    mixture of experts as a dense layer: g = min(x Wg^T, limit), u = clamp(x Wu^T, -limit, limit),
+    down(g sigmoid(alpha g) (u + 1)); gate and up keep their float32 sums up to the activation."""
 
     graph_safe = True
 
-    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
-        if activation != "silu":
-            raise UnsupportedError("activation other than SiLU")
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu",
+                 limit: float = 7.0, alpha: float = 1.702):
+        if activation not in ("silu", "clamped_gate"):
+            raise UnsupportedError(f"feed-forward activation {activation!r}")
+        self.activation, self.limit, self.alpha = activation, float(limit), float(alpha)
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.gate_up: Optional[LinearWeight] = None
         self.down: Optional[LinearWeight] = None
@@ -46,6 +50,10 @@ class GatedMLP(FeedForward):
         self.down = LinearWeight(weights["down_proj.weight"])
 
     def forward(self, x, ctx, residual):
+        if self.activation == "clamped_gate":
+            both = self.gate_up(x, out_dtype=torch.float32)
+            gated = ops.clamped_gate_mul(both, self.block, self.limit, self.alpha, out_dtype=x.dtype)
+            return self.down(gated, epilogue=ops.ADD, out=residual, ctx=ctx)
         if self.block == GATE_BLOCK and self.gate_up.supports_fused_gate(x.dtype):
             gated = self.gate_up(x, epilogue=ops.SILU_GATE)
         else:

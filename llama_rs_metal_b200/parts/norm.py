@@ -40,3 +40,14 @@ class RMSNorm(Norm):
         # partial sums a product left for the residual stream are added in the same pass
         pending = ctx.take_pending()
         return ops.rms_norm(hidden, self.weight, self.eps, ctx.runtime.dtype, rows=rows, partials=pending)
+
+    def add_into(self, hidden, y, ctx, mult=1.0, then=None):
+        # one pass: the sublayer's output is normalized, scaled and added to the stream, and the
+        # updated row goes through the next sublayer's norm while it is still in registers
+        fused = isinstance(then, RMSNorm) and then.weight.dtype == self.weight.dtype
+        out = ops.rms_norm_add_(hidden, y, self.weight, self.eps, mult,
+                                then.weight if fused else None, then.eps if fused else None,
+                                ctx.runtime.dtype if fused else None)
+        if then is not None and not fused:
+            out = then.forward(hidden, ctx)
+        return out

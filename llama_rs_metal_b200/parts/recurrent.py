@@ -8,6 +8,11 @@ update it token by token and read it out with the query (csrc/recurrent_scan.cu)
 * `gated_delta_rule`: S <- diag(g) S; S <- S + k (b (v - S^T k))^T with decays g per key channel
   and step sizes b computed from the input; q, k, v pass a short causal convolution first.
 
+A third keeps one number per channel (csrc/gated_recurrence.cu):
+
+* `gated_linear_recurrence`: S <- a S + sqrt(1 - a^2) (i u) with a decay a and an input gate i
+  computed from the input, block by block of channels; u passes a short causal convolution first.
+
 A step of any size (a prompt, a portion, one token) runs the same scan from the state the
 steps before left, so nothing depends on how a sequence was cut into steps.
 """
@@ -171,4 +176,64 @@ class GatedDeltaRule(Mixer):
         o = ops.linear_state_scan(q, k, v, state.state, ctx.cu_seqlens, ctx.slots, g=g, beta=beta)
         mixed = ops.head_norm_gate(o, self.eps, projected.dtype, weight=self.norm_weight, gate=both,
                                    gate_column=H * d, gate_act=ops.GATE_SIGMOID, out_scale=self.output_scale)
+        return self.out(mixed, epilogue=ops.ADD, out=residual, ctx=ctx)
+
+
+@register_mixer("gated_linear_recurrence")
+class GatedLinearRecurrence(Mixer):
+    """Two branches of `channels` channels each: y = gelu_tanh(W_y x + b_y) and
+    u = conv(W_x x + b_x), a causal convolution of `conv_taps` taps per channel with a bias (zeros
+    before the start, no activation). The channels are cut into `blocks` equal blocks; per block,
+    with square matrices of its own, r = sigmoid(A u + b_a) and i = sigmoid(B u + b_b). Then
+        a = exp(-decay_factor * r * softplus(lam)),   S <- a S + sqrt(1 - a^2) (i u)
+    per channel, from S = 0, and the output is W_o (S y). Gates, decays and the state are float32;
+    the projections keep their float32 sums up to the biases.
+    State: S [channels] in float32 and the last conv_taps - 1 convolution inputs of every channel."""
+
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, channels: int, blocks: int, conv_taps: int, decay_factor: float = 8.0):
+        if channels <= 0 or blocks <= 0 or channels % blocks or conv_taps <= 0:
+            raise InvalidError("gated linear recurrence: channels must be a multiple of blocks, and taps positive")
+        self.hidden_size, self.channels, self.blocks, self.conv_taps = hidden_size, channels, blocks, conv_taps
+        self.decay_factor = float(decay_factor)
+        self.fused: Optional[LinearWeight] = None
+        self.out: Optional[LinearWeight] = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        C, h, B, n = self.channels, self.hidden_size, self.blocks, self.conv_taps
+        s = C // B
+        return {"x_proj.weight": TensorSpec((C, h)), "x_proj.bias": TensorSpec((C,)),
+                "y_proj.weight": TensorSpec((C, h)), "y_proj.bias": TensorSpec((C,)),
+                "conv.weight": TensorSpec((C, n)), "conv.bias": TensorSpec((C,)),
+                "decay_gate.weight": TensorSpec((B, s, s)), "decay_gate.bias": TensorSpec((B, s)),
+                "input_gate.weight": TensorSpec((B, s, s)), "input_gate.bias": TensorSpec((B, s)),
+                "lam": TensorSpec((C,)), "o_proj.weight": TensorSpec((h, C))}
+
+    def bind(self, weights, runtime) -> None:
+        f32 = torch.float32
+        # x | y in one product; a block's two gate matrices one above the other in one block product
+        self.fused = LinearWeight(torch.cat([weights["x_proj.weight"], weights["y_proj.weight"]], dim=0))
+        self.in_bias = torch.cat([weights["x_proj.bias"], weights["y_proj.bias"]]).to(f32).contiguous()
+        self.taps = weights["conv.weight"].to(f32).contiguous()
+        self.conv_bias = weights["conv.bias"].to(f32).contiguous()
+        self.gates = torch.cat([weights["decay_gate.weight"], weights["input_gate.weight"]], dim=1).contiguous()
+        self.gate_bias = torch.cat([weights["decay_gate.bias"], weights["input_gate.bias"]], dim=1).to(f32).contiguous()
+        self.rate = (self.decay_factor * torch.nn.functional.softplus(weights["lam"].to(f32))).contiguous()
+        self.out = LinearWeight(weights["o_proj.weight"])
+
+    def cache_request(self):
+        return CompositeRequest((StateRequest((self.channels,), torch.float32),
+                                 StateRequest((self.conv_taps - 1, self.channels), torch.float32)))
+
+    def forward(self, x, ctx, cache, residual):
+        _needs_own_state(ctx)
+        C = self.channels
+        state, tails = cache
+        projected = self.fused(x, out_dtype=torch.float32)                       # [T, x | y], float32
+        u = ops.short_conv(projected, 0, C, self.in_bias[:C], self.taps, self.conv_bias, tails.state,
+                           ctx.cu_seqlens, ctx.seq_of_token, ctx.slots, x.dtype)
+        gates = ops.blockwise_linear(u, self.gates, bias=self.gate_bias, out_dtype=torch.float32)
+        mixed = ops.gated_linear_scan(u, gates, projected, C, self.in_bias[C:], self.rate, state.state,
+                                      ctx.cu_seqlens, ctx.slots, ctx.max_seq_len, self.blocks)
         return self.out(mixed, epilogue=ops.ADD, out=residual, ctx=ctx)

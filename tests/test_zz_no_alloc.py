@@ -42,8 +42,8 @@ def run(lib, symbol, q, k, v, table, slots, lens, splits, scratch=None):
         args.append(p(scratch))
     args += [p(out), p(table), table.shape[1], p(slots), p(lens), B, Hq, k.shape[1], d, 64,
              ctypes.c_float(d ** -0.5), 0, splits]
-    if scratch is not None:  # the ordinary entry point also takes a distance penalty and an output scale
-        args += [None, ctypes.c_float(1.0)]
+    if scratch is not None:  # the ordinary entry point also takes a distance penalty, an output scale, sinks and a temperature
+        args += [None, ctypes.c_float(1.0), None, ctypes.c_float(0.0), 0]
     args.append(stream)
     torch.cuda.synchronize()
     before, free_before = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]

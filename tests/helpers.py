@@ -136,6 +136,79 @@ def make_kikalix_dir(path, name, dtype=torch.bfloat16, steady_routing=False):
     return write_model_folder(path, config.to_dict(), tensors, spec["seed"])
 
 
+# Tiny Pibuvik configurations. P1: odd sizes throughout (no size a multiple of 16; a latent layer
+# with a window shorter than a page, a second one that reads the first one's latent through a window
+# longer than a page with other head sizes; grouped keys; a recurrence of three blocks and one of a
+# single block and a single tap; layers without a feed-forward). P2: head sizes 64 so that bfloat16
+# runs the tensor-core products and the tiled attention kernels with sinks and the temperature; a
+# window of exactly one page. P3: nothing optional (no feed-forward, no temperature, no mask, no
+# scales), as many key heads as query heads.
+def _dense(ff, limit):
+    return dict(kind="dense", ff=ff, limit=limit)
+
+
+def _latent(heads, dim, rot_dim, vdim, kv_rank, q_rank, scale, base, window=None, kv_from=None):
+    out = dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=kv_rank, q_rank=q_rank, scale=scale,
+               rot=dict(dims=rot_dim, base=base))
+    if window is not None:
+        out["mask"] = dict(size=window)
+    if kv_from is not None:
+        out["kv_from"] = kv_from
+    return out
+
+
+PIBUVIK = {
+    "P1": dict(
+        config=dict(architecture="Pibuvik", vocab=211, width=72, norm=dict(eps=1e-6), residual_mult=0.7,
+                    embedding=dict(scale=1.5), logit_scale=0.3, layers=[
+            dict(type="latent_attention", mixer=_latent(3, 12, 6, 10, 20, 28, 0.3, 100.0, window=7), mlp=_dense(40, 0.8)),
+            dict(type="attention", mixer=dict(heads=4, kv_heads=2, dim=12, vdim=12, scale=0.4,
+                                              q_temp=dict(coef=0.3, every=5)), mlp=None),
+            dict(type="rglru", mixer=dict(width=48, blocks=3, conv=3), mlp=_dense(56, 1.5)),
+            dict(type="latent_attention", mixer=_latent(2, 8, 6, 16, 20, 12, 0.5, 100.0, window=70, kv_from=0), mlp=None),
+            dict(type="rglru", mixer=dict(width=40, blocks=1, conv=1), mlp=None),
+        ]), seed=31, std=0.12),
+    "P2": dict(
+        config=dict(architecture="Pibuvik", vocab=512, width=320, norm=dict(eps=2e-5), residual_mult=0.4,
+                    embedding=dict(scale=2.0), logit_scale=0.5, layers=[
+            dict(type="attention", mixer=dict(heads=8, kv_heads=2, dim=64, vdim=64, scale=0.125,
+                                              q_temp=dict(coef=0.25, every=48)), mlp=_dense(384, 2.0)),
+            dict(type="rglru", mixer=dict(width=256, blocks=4, conv=4), mlp=_dense(384, 2.0)),
+            dict(type="latent_attention", mixer=_latent(4, 64, 32, 64, 96, 128, 0.1, 10000.0, window=100), mlp=_dense(384, 2.0)),
+            dict(type="latent_attention", mixer=_latent(4, 32, 32, 32, 96, 64, 0.15, 10000.0, window=64, kv_from=2), mlp=None),
+        ]), seed=32, std=0.06),
+    "P3": dict(
+        config=dict(architecture="Pibuvik", vocab=300, width=64, norm=dict(eps=1e-5), layers=[
+            dict(type="rglru", mixer=dict(width=64, blocks=2, conv=2), mlp=None),
+            dict(type="attention", mixer=dict(heads=2, kv_heads=2, dim=24, vdim=24, scale=0.2), mlp=None),
+            dict(type="latent_attention", mixer=_latent(1, 16, 8, 24, 12, 16, 0.25, 50.0), mlp=None),
+        ]), seed=33, std=0.15),
+}
+
+
+def make_pibuvik_dir(path, name, dtype=torch.bfloat16):
+    """A model folder of a tiny Pibuvik configuration (a name of PIBUVIK, or a spec of the caller's
+    own) with seeded random weights. Norm weights are N(1, 0.2); biases, sinks and the other
+    vectors N(0, 0.5); the recurrence's rates N(-3, 1), so that some channels forget at once and
+    others carry their state over hundreds of tokens."""
+    from llama_rs_metal_b200.engine.model import DecoderModel
+    from llama_rs_metal_b200.registry import find_architecture
+    from llama_rs_metal_b200.runtime import Runtime
+    from llama_rs_metal_b200.weights.random_init import random_tensors, write_model_folder
+    spec = PIBUVIK[name] if isinstance(name, str) else name
+    arch = find_architecture(spec["config"])
+    config = arch.config_class.from_dict(spec["config"])
+    model = DecoderModel(arch.plan(config), Runtime(torch.device("cpu"), torch.float32))
+    tensors = random_tensors(model.tensor_specs(), spec["seed"], std=spec["std"], vector_mean=0.0, vector_std=0.5,
+                             dtype=dtype)
+    for name_, t in tensors.items():
+        if "norm" in name_.rsplit(".", 1)[-1]:
+            t.mul_(0.4).add_(1.0)
+        if name_.endswith(".lam"):   # decays from about 0.3 to 0.97 per token: some channels remember far back
+            t.mul_(2.0).sub_(3.0)
+    return write_model_folder(path, config.to_dict(), tensors, spec["seed"])
+
+
 def random_tokens(seed, length, vocab):
     rng = np.random.default_rng(seed)
     return [int(t) for t in rng.integers(0, vocab, size=length)]

@@ -148,7 +148,7 @@ def latent_attention(h, w, p, m, eps, kept):
     k_plain = (c @ w[p + "uk"].T).reshape(T, H, d)
     v = (c @ w[p + "uv"].T).reshape(T, H, dv)
     gate = torch.sigmoid(h @ w[p + "g"].T)
-    window = m["mask"]["size"]
+    window = m["mask"]["size"] if "mask" in m else T   # without a mask every earlier position is seen
     out = torch.zeros(T, H, dv, dtype=F64)
     for head in range(H):
         for t in range(T):

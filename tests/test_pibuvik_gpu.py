@@ -489,15 +489,15 @@ def test_sinks_temperature_and_a_far_key(dtype, H, G, d):
     gen = torch.Generator().manual_seed(H * d)
     T, far = 700, 67
     q = torch.randn(T, H, d, generator=gen)
-    k = torch.randn(T, G, d, generator=gen)
+    k = torch.randn(T, G, d, generator=gen) * 0.3
     direction = torch.randn(d, generator=gen)
     direction /= direction.norm()
     q[600:] = q[600:] * 0.3 + 6.0 * direction             # late queries look for the far key
     k[far] = 4.0 * direction
     q, k = q.to(dtype), k.to(dtype)
     sinks = torch.linspace(-2.0, 1.0, H)
-    sinks[0] = 9.0
-    temperature, scale = (0.4, 50), 1.0 / math.sqrt(d)
+    sinks[0] = 25.0                                        # about the far key's score: it takes half of head 0
+    temperature, scale = (0.4, 50), 0.5
     want = plain_attention(q.to(F64), k.to(F64), k.to(F64), scale, None, sinks.to(F64), temperature)
     plain_weight = plain_attention(q[650:651].to(F64), k.to(F64), torch.eye(T, dtype=F64)[:, None, :].expand(T, G, T),
                                    scale, None, sinks.to(F64), temperature, first_query=650)

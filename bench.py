@@ -225,10 +225,41 @@ DESIGN_SIZES = {   # width, heads, kv heads, expert width, experts, chosen, wind
 }
 
 
+def pibuvik_shape(width, heads, kv_heads, ff, kv_rank, window, layers, vocab=32768):
+    """A Pibuvik configuration with layers of a real model's widths (head size 128): a gated linear
+    recurrence, attention with sinks, latent attention, and latent attention that reads the
+    layer before it, in turn; a dense feed-forward behind each."""
+    d = 128
+    mlp = dict(kind="dense", ff=ff, limit=7.0)
+    latent = dict(heads=heads, dim=d - 32, rot_dim=32, vdim=d, kv_rank=kv_rank, q_rank=width // 2, scale=d ** -0.5,
+                  rot=dict(dims=32, base=10000.0), mask=dict(size=window))
+    kinds = [
+        dict(type="rglru", mixer=dict(width=width, blocks=heads, conv=4), mlp=mlp),
+        dict(type="attention", mixer=dict(heads=heads, kv_heads=kv_heads, dim=d, vdim=d, scale=d ** -0.5,
+                                          q_temp=dict(coef=0.1, every=1024)), mlp=mlp),
+        dict(type="latent_attention", mixer=latent, mlp=mlp),
+        dict(type="latent_attention", mixer=dict(latent, kv_from=2), mlp=mlp),
+    ]
+    chosen = [dict(kinds[i % 4]) for i in range(layers)]
+    for i, layer in enumerate(chosen):
+        if "kv_from" in layer["mixer"]:
+            layer["mixer"] = dict(layer["mixer"], kv_from=i - 1)
+    return dict(architecture="Pibuvik", vocab=vocab, width=width, norm=dict(eps=1e-5), residual_mult=0.5,
+                embedding=dict(scale=1.0), logit_scale=1.0, layers=chosen)
+
+
+PIBUVIK_SIZES = {   # width, heads, kv heads, feed-forward width, latent width, window, layers
+    "1k": (1024, 8, 2, 4096, 128, 512, 4),
+    "2k": (2048, 16, 4, 8192, 256, 1024, 4),
+    "4k": (4096, 32, 8, 14336, 256, 2048, 4),
+}
+
+
 def design_bench(args) -> int:
-    """Prefill and decode throughput of the Kikalix design at a few layer sizes, beside the Llama
-    decoder at equal size (the same width, head geometry, vocabulary and number of layer runs; its
-    feed-forward as wide as the experts a token uses). Random weights, one GPU, bfloat16."""
+    """Prefill and decode throughput of the Kikalix or the Pibuvik design at a few layer sizes, beside
+    the Llama decoder at equal size (the same width, head geometry, vocabulary and number of layer
+    runs; its feed-forward as wide as the experts a token uses, or as the dense one). Random
+    weights, one GPU, bfloat16."""
     if args.profile:
         os.environ["LRM_PROFILE"] = "1"
     import numpy as np
@@ -241,6 +272,7 @@ def design_bench(args) -> int:
     rng = np.random.default_rng(0)
     prompt, batch, steps = args.prefill_tokens or PREFILL_TOKENS, args.batch or 8, min(args.steps, 64)
     sizes = [args.design_size] if args.design_size else list(DESIGN_SIZES)
+    design_name = args.design.capitalize()
     out = {}
 
     def measure(model, vocab, name):
@@ -291,24 +323,32 @@ def design_bench(args) -> int:
                 "weight_gb": round(model.weight_bytes / 1e9, 3)}
 
     for size in sizes:
-        width, heads, kv_heads, ff, experts, top, window, layers = DESIGN_SIZES[size]
-        config = kikalix_shape(width, heads, kv_heads, ff, experts, top, window, layers)
-        runs = layers + 2
-        model = engine.random(config, seed=0, std=0.02, norm_mean=0.0)
-        row = {"kikalix": measure(model, config["vocab"], f"Kikalix {size}")}
+        if args.design == "pibuvik":
+            width, heads, kv_heads, ff, kv_rank, window, layers = PIBUVIK_SIZES[size]
+            config = pibuvik_shape(width, heads, kv_heads, ff, kv_rank, window, layers)
+            runs, twin_ff, norm_mean = layers, ff, 1.0
+            shape = dict(width=width, heads=heads, kv_heads=kv_heads, head_dim=128, ff=ff, kv_rank=kv_rank,
+                         window=window, layers=layers)
+        else:
+            width, heads, kv_heads, ff, experts, top, window, layers = DESIGN_SIZES[size]
+            config = kikalix_shape(width, heads, kv_heads, ff, experts, top, window, layers)
+            runs, twin_ff, norm_mean = layers + 2, top * ff, 0.0
+            shape = dict(width=width, heads=heads, kv_heads=kv_heads, head_dim=128, expert_ff=ff, experts=experts,
+                         top=top, window=window, layer_runs=runs)
+        model = engine.random(config, seed=0, std=0.02, norm_mean=norm_mean)
+        row = {args.design: measure(model, config["vocab"], f"{design_name} {size}")}
         del model
         torch.cuda.empty_cache()
-        twin = llama(width, top * ff, runs, heads, kv_heads, 128, 8.0, False)
+        twin = llama(width, twin_ff, runs, heads, kv_heads, 128, 8.0, False)
         twin["vocab_size"] = config["vocab"]
         model = engine.random(twin, seed=0, std=0.02)
         row["llama_equal_size"] = measure(model, twin["vocab_size"], f"Llama {size}")
         del model
         torch.cuda.empty_cache()
-        row["shape"] = dict(width=width, heads=heads, kv_heads=kv_heads, head_dim=128, expert_ff=ff, experts=experts,
-                            top=top, window=window, layer_runs=runs)
+        row["shape"] = shape
         out[size] = row
     print(json.dumps({"metric": f"prefill tok/s (one {prompt}-token prompt) and decode tok/s (batch {batch} at "
-                                f"{prompt} tokens), Kikalix beside Llama at equal size",
+                                f"{prompt} tokens), {design_name} beside Llama at equal size",
                       "dtype": "bf16", "data": "synthetic token ids, random-init weights", "n_gpus": 1,
                       "decode_steps": steps, "peaks": peak_source, "cuda_graph": not args.profile, "sizes": out}))
     return 0
@@ -341,7 +381,7 @@ def main() -> int:
     parser.add_argument("--profile", action="store_true",
                         help="time every kernel launch (LRM_PROFILE=1) and print the table to stderr; the "
                              "line's numbers are then those of unfused, uncaptured launches")
-    parser.add_argument("--design", choices=["kikalix"], default=None,
+    parser.add_argument("--design", choices=["kikalix", "pibuvik"], default=None,
                         help="instead of the default workload: prefill and decode throughput of this design at "
                              "a few layer sizes beside the Llama decoder at equal size (see design_bench)")
     parser.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default=None,

@@ -4,7 +4,7 @@
 //   acc = acc e^(m-m') + e^(s-m') v;  out = acc / l
 // (reference: crates/metal-backend/src/shaders/attention.metal:28-57).
 // It is the attention of the float32 path for prompts and for decoding, and
-// the bfloat16 path's fallback for sizes its tiled kernels refuse. The two
+// the bfloat16 path's fallback for sizes its tiled kernels refuse (head sizes up to 1024). The two
 // entry points differ only in where keys come from (the step's packed k/v, or
 // the paged cache), so a prompt, its token-by-token replay and its replay in
 // chunks of any size do the same arithmetic in the same order. The paged entry
@@ -23,7 +23,7 @@
 // that are the first dv columns of the key rows are read from the keys' storage with the keys' d.
 #include "common.cuh"
 
-constexpr int kMaxPerLane = 16;  // head_dim <= 512
+constexpr int kWidest = 32;  // elements of a row one lane holds at most: head sizes up to 1024
 
 struct PackedKeys {
   const void* k;
@@ -53,14 +53,15 @@ struct PagedKeys {
   }
 };
 
-template <typename A, typename Keys>
+// PER: elements of a query (and of the output) one lane keeps in registers; d, dv <= 32 * PER.
+template <typename A, int PER, typename Keys>
 __device__ void attend_row(const A* __restrict__ q, A* __restrict__ out, const Keys& keys, int kh,
                            int first, int last, int d, int dv, float scale, float slope,
                            float out_scale, float sink) {
   const int lane = threadIdx.x & 31;
-  float qv[kMaxPerLane], acc[kMaxPerLane];
+  float qv[PER], acc[PER];
 #pragma unroll
-  for (int i = 0; i < kMaxPerLane; ++i) {
+  for (int i = 0; i < PER; ++i) {
     const int j = lane + 32 * i;
     qv[i] = j < d ? to_f32(q[j]) : 0.f;
     acc[i] = 0.f;
@@ -72,7 +73,7 @@ __device__ void attend_row(const A* __restrict__ q, A* __restrict__ out, const K
     const A* vr = keys.template value<A>(p, kh);
     float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < kMaxPerLane; ++i) {
+    for (int i = 0; i < PER; ++i) {
       const int j = lane + 32 * i;
       if (j < d) dot = fmaf(qv[i], to_f32(kr[j]), dot);
     }
@@ -82,14 +83,14 @@ __device__ void attend_row(const A* __restrict__ q, A* __restrict__ out, const K
     const float old = expf(m - nm), prob = expf(s - nm);
     l = fmaf(l, old, prob);
 #pragma unroll
-    for (int i = 0; i < kMaxPerLane; ++i) {
+    for (int i = 0; i < PER; ++i) {
       const int j = lane + 32 * i;
       if (j < dv) acc[i] = fmaf(prob, to_f32(vr[j]), __fmul_rn(acc[i], old));
     }
     m = nm;
   }
 #pragma unroll
-  for (int i = 0; i < kMaxPerLane; ++i) {
+  for (int i = 0; i < PER; ++i) {
     const int j = lane + 32 * i;
     if (j < dv) out[j] = from_f32<A>(out_scale == 1.0f ? acc[i] / l : (acc[i] / l) * out_scale);
   }
@@ -99,7 +100,7 @@ __device__ __forceinline__ float query_temperature(int pos, float coef, int ever
   return every > 0 ? 1.0f + coef * logf(static_cast<float>((pos + 1) / every + 1)) : 1.0f;
 }
 
-template <typename A>
+template <typename A, int PER>
 __global__ void attention_packed_kernel(const A* __restrict__ q, const A* __restrict__ k,
                                         const A* __restrict__ v, A* __restrict__ out,
                                         const int* __restrict__ cu_seqlens,
@@ -114,12 +115,12 @@ __global__ void attention_packed_kernel(const A* __restrict__ q, const A* __rest
   const int first = window > 0 ? max(0, pos - window + 1) : 0;
   PackedKeys keys{k, v, static_cast<size_t>(start), kv_heads, d, v_stride};
   const size_t row = static_cast<size_t>(t) * q_heads + h;
-  attend_row<A>(q + row * d, out + row * dv, keys, h / (q_heads / kv_heads), first, pos, d, dv,
+  attend_row<A, PER>(q + row * d, out + row * dv, keys, h / (q_heads / kv_heads), first, pos, d, dv,
                 scale * query_temperature(pos, temp_coef, temp_every),
                 slopes != nullptr ? slopes[h] : 0.f, out_scale, sinks != nullptr ? sinks[h] : -INFINITY);
 }
 
-template <typename A>
+template <typename A, int PER>
 __global__ void attention_paged_kernel(const A* __restrict__ q, const A* __restrict__ k_pages,
                                        const A* __restrict__ v_pages, A* __restrict__ out,
                                        const int* __restrict__ page_table, int table_stride,
@@ -140,14 +141,14 @@ __global__ void attention_paged_kernel(const A* __restrict__ q, const A* __restr
   PagedKeys keys{k_pages, v_pages, page_table + static_cast<size_t>(slots[b]) * table_stride,
                  kv_heads, d, v_stride, page_size};
   const size_t row = static_cast<size_t>(t) * q_heads + h;
-  attend_row<A>(q + row * d, out + row * dv, keys, h / (q_heads / kv_heads), first, pos, d, dv,
+  attend_row<A, PER>(q + row * d, out + row * dv, keys, h / (q_heads / kv_heads), first, pos, d, dv,
                 scale * query_temperature(pos, temp_coef, temp_every),
                 slopes != nullptr ? slopes[h] : 0.f, out_scale, sinks != nullptr ? sinks[h] : -INFINITY);
 }
 
 static bool bad_geometry(int q_heads, int kv_heads, int d, int dv) {
   return q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || d <= 0 ||
-         d > 32 * kMaxPerLane || dv <= 0 || dv > 32 * kMaxPerLane;
+         d > 32 * kWidest || dv <= 0 || dv > 32 * kWidest;
 }
 
 LRM_API int lrm_attention_packed_rowwise(const void* q, const void* k, const void* v, void* out,
@@ -161,19 +162,26 @@ LRM_API int lrm_attention_packed_rowwise(const void* q, const void* k, const voi
   if (bad_geometry(q_heads, kv_heads, d, dv)) return LRM_BAD_ARGUMENT;
   if (q_heads > 65535) return LRM_UNSUPPORTED;
   const dim3 grid(tokens, q_heads);
+  const int widest = d > dv ? d : dv;
+#define LRM_PACKED(AT, PER)                                                                                      \
+  attention_packed_kernel<AT, PER><<<grid, 32, 0, stream>>>(                                                     \
+      static_cast<const AT*>(q), static_cast<const AT*>(k), static_cast<const AT*>(v), static_cast<AT*>(out),    \
+      cu_seqlens, seq_of_token, q_heads, kv_heads, d, dv, scale, window, slopes, out_scale, sinks, temp_coef,    \
+      temp_every, v_stride)
+#define LRM_PACKED_BY_WIDTH(AT)                  \
+  do {                                           \
+    if (widest <= 128) LRM_PACKED(AT, 4);        \
+    else if (widest <= 512) LRM_PACKED(AT, 16);  \
+    else LRM_PACKED(AT, 32);                     \
+  } while (0)
   if (dtype == LRM_F32)
-    attention_packed_kernel<float><<<grid, 32, 0, stream>>>(
-        static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v),
-        static_cast<float*>(out), cu_seqlens, seq_of_token, q_heads, kv_heads, d, dv, scale, window,
-        slopes, out_scale, sinks, temp_coef, temp_every, v_stride);
+    LRM_PACKED_BY_WIDTH(float);
   else if (dtype == LRM_BF16)
-    attention_packed_kernel<__nv_bfloat16><<<grid, 32, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
-        static_cast<const __nv_bfloat16*>(v), static_cast<__nv_bfloat16*>(out), cu_seqlens,
-        seq_of_token, q_heads, kv_heads, d, dv, scale, window, slopes, out_scale, sinks, temp_coef,
-        temp_every, v_stride);
+    LRM_PACKED_BY_WIDTH(__nv_bfloat16);
   else
     return LRM_BAD_ARGUMENT;
+#undef LRM_PACKED_BY_WIDTH
+#undef LRM_PACKED
   LRM_LAUNCH_CHECK();
   return 0;
 }
@@ -196,20 +204,26 @@ LRM_API int lrm_attention_paged_rowwise(const void* q, const void* k_pages, cons
   if (positions == nullptr && kv_lens == nullptr) return LRM_BAD_ARGUMENT;
   if (q_heads > 65535) return LRM_UNSUPPORTED;
   const dim3 grid(queries, q_heads);
+  const int widest = d > dv ? d : dv;
+#define LRM_PAGED(AT, PER)                                                                                       \
+  attention_paged_kernel<AT, PER><<<grid, 32, 0, stream>>>(                                                      \
+      static_cast<const AT*>(q), static_cast<const AT*>(k_pages), static_cast<const AT*>(v_pages),               \
+      static_cast<AT*>(out), page_table, table_stride, slots, kv_lens, seq_of_token, positions, q_heads,         \
+      kv_heads, d, dv, page_size, scale, window, slopes, out_scale, sinks, temp_coef, temp_every, v_stride)
+#define LRM_PAGED_BY_WIDTH(AT)                  \
+  do {                                          \
+    if (widest <= 128) LRM_PAGED(AT, 4);        \
+    else if (widest <= 512) LRM_PAGED(AT, 16);  \
+    else LRM_PAGED(AT, 32);                     \
+  } while (0)
   if (dtype == LRM_F32)
-    attention_paged_kernel<float><<<grid, 32, 0, stream>>>(
-        static_cast<const float*>(q), static_cast<const float*>(k_pages),
-        static_cast<const float*>(v_pages), static_cast<float*>(out), page_table, table_stride,
-        slots, kv_lens, seq_of_token, positions, q_heads, kv_heads, d, dv, page_size, scale, window,
-        slopes, out_scale, sinks, temp_coef, temp_every, v_stride);
+    LRM_PAGED_BY_WIDTH(float);
   else if (dtype == LRM_BF16)
-    attention_paged_kernel<__nv_bfloat16><<<grid, 32, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
-        static_cast<const __nv_bfloat16*>(v_pages), static_cast<__nv_bfloat16*>(out), page_table,
-        table_stride, slots, kv_lens, seq_of_token, positions, q_heads, kv_heads, d, dv, page_size,
-        scale, window, slopes, out_scale, sinks, temp_coef, temp_every, v_stride);
+    LRM_PAGED_BY_WIDTH(__nv_bfloat16);
   else
     return LRM_BAD_ARGUMENT;
+#undef LRM_PAGED_BY_WIDTH
+#undef LRM_PAGED
   LRM_LAUNCH_CHECK();
   return 0;
 }

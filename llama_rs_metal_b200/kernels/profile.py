@@ -103,6 +103,21 @@ WORK: Dict[str, Callable[..., Tuple[float, float]]] = {
     "lrm_moe_router": lambda a: (_v(a[7]) * _v(a[8]) * _ELEM[_v(a[1])] + 4.0 * _v(a[9]) * _v(a[8]), 2.0 * _v(a[7]) * _v(a[8]) * _v(a[9])),
     "lrm_moe_route": lambda a: (_v(a[4]) * (_v(a[5]) * 4.0 + _v(a[6]) * 8.0), 0),
     "lrm_add_row": lambda a: (8.0 * _v(a[2]) * _v(a[3]), 0),
+    # the norm behind a sublayer: its output read, the stream read and written, the next norm's result written
+    "lrm_rms_norm_add": lambda a: (_v(a[10]) * _v(a[11]) * (12.0 + (_ELEM[_v(a[8])] if a[7].value else 0)),
+                                   8.0 * _v(a[10]) * _v(a[11])),
+    "lrm_clamped_gate_mul": lambda a: (_v(a[4]) * _v(a[5]) * (2.0 * _ELEM[_v(a[1])] + _ELEM[_v(a[3])]), 0),
+    "lrm_short_conv": lambda a: (_v(a[14]) * _v(a[16]) * (_ELEM[_v(a[1])] + _ELEM[_v(a[13])]), 2.0 * _v(a[14]) * _v(a[16]) * _v(a[7])),
+    # the recurrence: per token and channel the convolved input, two gates, the read-out branch, the result
+    "lrm_gated_linear_scan": lambda a: (hints["tokens"] * _v(a[14]) * (2.0 * _ELEM[_v(a[1])] + 12.0) + 8.0 * _v(a[12]) * _v(a[14]),
+                                        30.0 * hints["tokens"] * _v(a[14])),
+    "lrm_blockwise_linear": lambda a: (
+        _v(a[12]) * _v(a[13]) * (_v(a[15]) * _ELEM[_v(a[1])] + _v(a[14]) * _ELEM[_v(a[9])])
+        + _v(a[13]) * _v(a[14]) * _v(a[15]) * _ELEM[_v(a[5])], 2.0 * _v(a[12]) * _v(a[13]) * _v(a[14]) * _v(a[15])),
+    "lrm_rope_heads": lambda a: (2.0 * _v(a[10]) * _v(a[11]) * _v(a[9]) * _ELEM[_v(a[1])], 0),
+    "lrm_latent_prepare": lambda a: (
+        _v(a[21]) * ((_v(a[4]) + (_v(a[7]) + _v(a[9]) if _v(a[6]) >= 0 else 0)) * (_ELEM[_v(a[1])] + _ELEM[_v(a[20])])
+                     + 8.0 * _v(a[18])), 0),
     "lrm_sample_gumbel_rows": lambda a: (4.0 * _v(a[4]) * _v(a[5]), 0),
 }
 # entry points that only answer questions and launch nothing

@@ -9,7 +9,8 @@ A bfloat16 decode step of a layer that writes its own unwindowed cache runs rota
 cache write, attention and the merge of the splits as one cluster kernel
 (csrc/attention_decode_cluster.cu). A step that appends several tokens to started
 sequences stores its keys first and attends over the cache (row-wise, or the tiled
-extend kernel in bfloat16).
+extend kernel in bfloat16). bfloat16 attention over one key head whose rows also hold the
+values (latent attention's cache) runs csrc/attention_shared_keys.cu in every phase.
 
 `attend` is the one call a mixer makes: it takes the step's projection and picks
 rotation, cache write and attention kernels for the step's phase and geometry.
@@ -66,6 +67,14 @@ def _value_stride(kv) -> int:
     return kv.k.shape[3] if getattr(kv, "values_in_keys", False) else kv.v.shape[3]
 
 
+def _shared_keys(q, kv_heads: int, dv: int, slopes, out_scale: float, extras) -> bool:
+    """True when the kernel for one key head whose rows hold the values (latent attention's cache
+    layout, csrc/attention_shared_keys.cu) takes this attention."""
+    return (not force_rowwise and q.dtype == torch.bfloat16 and kv_heads == 1 and slopes is None
+            and out_scale == 1.0 and extras.plain and q.data_ptr() % 16 == 0
+            and bool(library.load().lrm_attention_shared_keys_supports(q.shape[1], q.shape[2], dv, 64)))
+
+
 def _tiled(q, page_size: int) -> bool:
     return (not force_rowwise and q.dtype == torch.bfloat16
             and bool(library.load().lrm_attention_tiled_supports(q.shape[2], page_size)))
@@ -86,6 +95,12 @@ def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: flo
     if v is None or not extras.plain:
         dv = value_dim if v is None else v.shape[2]
         shared = v is None or v.data_ptr() == k.data_ptr()
+        if shared and dv != d and k.data_ptr() % 16 == 0 and _shared_keys(q, k.shape[1], dv, slopes, out_scale, extras):
+            _done(lib.lrm_attention_shared_keys(_ptr(q), _ptr(k), None, _ptr(out), _ptr(cu_seqlens), None, None, 0,
+                                                None, cu_seqlens.numel() - 1, max_seq_len, Hq, d, dv,
+                                                ctypes.c_float(scale), window, _stream()),
+                  "attention_shared_keys")
+            return
         if dv == d and _tiled(q, 64) and shared:
             _done(lib.lrm_attention_prefill_tiled(_ptr(q), _ptr(k), _ptr(k), _ptr(out), _ptr(cu_seqlens),
                                                   cu_seqlens.numel() - 1, max_seq_len, Hq, k.shape[1], d,
@@ -165,6 +180,13 @@ def decode(q, kv, out, slots, kv_lens, max_kv_len: int, scale: float, window: in
     dv = _value_dim(kv)
     extras = extras or NO_EXTRAS
     lib = library.load()
+    if (getattr(kv, "values_in_keys", False) and dv != d and kv.page_size == 64
+            and _shared_keys(q, kv.kv_heads, dv, slopes, out_scale, extras)):
+        _done(lib.lrm_attention_shared_keys(_ptr(q), None, _ptr(kv.k), _ptr(out), None, _ptr(kv_lens),
+                                            _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots), B, 1, Hq, d,
+                                            dv, ctypes.c_float(scale), window, _stream()),
+              "attention_shared_keys")
+        return
     if dv == d and _tiled(q, kv.page_size):
         splits = decode_splits(B, kv.kv_heads, Hq // kv.kv_heads, max_kv_len, window)
         partials = torch.empty((B, Hq, splits, d + 2), dtype=torch.float32, device=q.device)
@@ -192,6 +214,14 @@ def extend(q, kv, out, cu_seqlens, seq_of_token, positions, slots, kv_lens, max_
     dv = _value_dim(kv)
     extras = extras or NO_EXTRAS
     lib = library.load()
+    if (getattr(kv, "values_in_keys", False) and dv != d and kv.page_size == 64
+            and _shared_keys(q, kv.kv_heads, dv, slopes, out_scale, extras)):
+        _done(lib.lrm_attention_shared_keys(_ptr(q), None, _ptr(kv.k), _ptr(out), _ptr(cu_seqlens), _ptr(kv_lens),
+                                            _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
+                                            cu_seqlens.numel() - 1, max_seq_len, Hq, d, dv, ctypes.c_float(scale),
+                                            window, _stream()),
+              "attention_shared_keys")
+        return
     if dv == d and _tiled(q, kv.page_size):
         _done(lib.lrm_attention_extend_tiled(_ptr(q), _ptr(kv.k), _ptr(kv.v), _ptr(out), _ptr(cu_seqlens),
                                              _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),

@@ -78,6 +78,11 @@ WORK: Dict[str, Callable[..., Tuple[float, float]]] = {
     "lrm_attention_paged_rowwise": lambda a: (2.0 * hints["kv_tokens"] * _v(a[13]) * _v(a[14]) * _ELEM[_v(a[4])], 0),
     "lrm_attention_extend_tiled": lambda a: (2.0 * hints["kv_tokens"] * _v(a[12]) * _v(a[13]) * 2,
                                              4.0 * hints["pairs"] * _v(a[11]) * _v(a[13])),
+    # one shared key head whose rows hold the values: the keys once per sequence; per (query, key) pair and
+    # head a dot product of dk and a weighted sum of dv (the hint counts the whole causal triangle, also
+    # where a window hides most of it)
+    "lrm_attention_shared_keys": lambda a: (2.0 * hints["kv_tokens"] * _v(a[12]),
+                                            2.0 * hints["pairs"] * _v(a[11]) * (_v(a[12]) + _v(a[13]))),
     "lrm_argmax_rows": lambda a: (4.0 * _v(a[4]) * _v(a[5]), 0),
     # the state scan: every sequence's state read and written once, the step's float32 inputs and outputs
     # once; per token and state element a decay, two (three with the delta rule) sums and the update

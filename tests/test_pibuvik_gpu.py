@@ -520,7 +520,8 @@ def test_sinks_temperature_and_a_far_key(dtype, H, G, d):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,width,dv,window", [(3, 26, 20, 7), (4, 128, 96, 64), (2, 40, 24, 65), (1, 24, 16, 1)])
+@pytest.mark.parametrize("H,width,dv,window", [(3, 26, 20, 7), (4, 128, 96, 64), (2, 40, 24, 65), (1, 24, 16, 1),
+                                               (6, 96, 64, 65), (16, 288, 256, 100), (20, 64, 48, 33), (2, 544, 512, 130)])
 def test_window_edges_over_keys_that_hold_their_values(dtype, H, width, dv, window):
     """One key head whose rows' first dv columns are the values (latent attention's cache). For
     chosen queries the key just inside the window and the key just outside it are both made to

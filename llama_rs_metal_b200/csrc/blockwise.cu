@@ -6,14 +6,98 @@
 // elements), so a block may be a part of a wider head and the result may land beside other
 // columns. Gates of a recurrence computed per block of channels, and the per-head matrices of
 // latent attention (a query head folded into the latent space, a head's output unfolded from
-// it), are such products. Sums are float32 in ascending order of the input index, whatever the
-// tiling, so a row's result does not depend on the rows beside it.
+// it), are such products. Sums are float32 in an order that depends on the input index only, so a
+// row's result does not depend on the rows beside it.
 //
 // rope_heads: copies `rot` columns of every head, rotated by position (pairs i, i + rot/2,
 // angle = float(position) * inv_freq[i]), from one strided layout to another.
-#include "common.cuh"
+// bfloat16 inputs whose blocks start on 16-byte boundaries (m a multiple of 8) run on the
+// warp-level tensor path: a CTA computes 64 tokens x 64 outputs of one block, 32 inputs at a time
+// through double-buffered shared tiles (cp.async, ldmatrix, mma.sync m16n8k16, float32 sums);
+// everything else, and float32, runs the plain tiled kernel.
+#include "attention_mma.cuh"
 
 namespace {
+
+constexpr int kMmaDepth = 32, kMmaStride = kMmaDepth + 8;
+
+template <typename O>
+__global__ __launch_bounds__(kThreads) void blockwise_linear_mma_kernel(
+    const __nv_bfloat16* __restrict__ x, long long x_row, long long x_block, const __nv_bfloat16* __restrict__ w,
+    const float* __restrict__ bias, const float* __restrict__ row_scale, O* __restrict__ out, long long out_row,
+    long long out_block, int T, int B, int n, int m) {
+  __shared__ __align__(16) __nv_bfloat16 xs[2][kTile * kMmaStride];
+  __shared__ __align__(16) __nv_bfloat16 ws[2][kTile * kMmaStride];
+  const int b = blockIdx.y, t0 = blockIdx.z * kTile, n0 = blockIdx.x * kTile;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const __nv_bfloat16* xb = x + static_cast<size_t>(b) * x_block;
+  const __nv_bfloat16* wb = w + static_cast<size_t>(b) * n * m;
+  auto issue = [&](int k0, int stage) {
+    for (int idx = threadIdx.x; idx < kTile * (kMmaDepth / 8); idx += kThreads) {
+      const int r = idx / (kMmaDepth / 8), c = 8 * (idx % (kMmaDepth / 8));
+      const bool in_k = k0 + c < m;
+      const bool x_ok = in_k && t0 + r < T, w_ok = in_k && n0 + r < n;
+      cp_async16(&xs[stage][r * kMmaStride + c], x_ok ? xb + static_cast<size_t>(t0 + r) * x_row + k0 + c : xb,
+                 x_ok ? 16 : 0);
+      cp_async16(&ws[stage][r * kMmaStride + c], w_ok ? wb + static_cast<size_t>(n0 + r) * m + k0 + c : wb,
+                 w_ok ? 16 : 0);
+    }
+    cp_async_commit();
+  };
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
+  pdl_wait();
+  const int steps = (m + kMmaDepth - 1) / kMmaDepth;
+  issue(0, 0);
+  for (int ki = 0; ki < steps; ++ki) {
+    const int stage = ki & 1;
+    if (ki + 1 < steps) {
+      issue((ki + 1) * kMmaDepth, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kMmaDepth / 16; ++kk) {
+      uint32_t a[4];
+      ldsm_x4(a[0], a[1], a[2], a[3],
+              &xs[stage][(16 * warp + (lane & 7) + 8 * ((lane >> 3) & 1)) * kMmaStride + 16 * kk + 8 * (lane >> 4)]);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(b0, b1, b2, b3,
+                &ws[stage][(16 * np + (lane & 7) + 8 * (lane >> 4)) * kMmaStride + 16 * kk + 8 * ((lane >> 3) & 1)]);
+        mma16816(acc[2 * np], a, b0, b1);
+        mma16816(acc[2 * np + 1], a, b2, b3);
+      }
+    }
+    __syncthreads();
+  }
+  pdl_trigger();
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int row = t0 + 16 * warp + g + 8 * half;
+    if (row >= T) continue;
+    const float scale = row_scale != nullptr ? row_scale[static_cast<size_t>(row) * B + b] : 1.0f;
+    O* dst = out + static_cast<size_t>(row) * out_row + static_cast<size_t>(b) * out_block;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int c = n0 + 8 * j + 2 * t + e;
+        if (c >= n) continue;
+        float v = acc[j][2 * half + e];
+        if (bias != nullptr) v += bias[static_cast<size_t>(b) * n + c];
+        if (row_scale != nullptr) v *= scale;
+        dst[c] = from_f32<O>(v);
+      }
+    }
+  }
+}
 
 constexpr int kRows = 32, kCols = 64, kDepth = 32;  // tile: 32 tokens x 64 outputs, 32 inputs at a time
 
@@ -105,6 +189,23 @@ LRM_API int lrm_blockwise_linear(const void* x, int x_dtype, long long x_row, lo
   if (blocks <= 0 || n <= 0 || m <= 0 || x == nullptr || w == nullptr || out == nullptr) return LRM_BAD_ARGUMENT;
   const int row_tiles = (tokens + kRows - 1) / kRows;
   if (blocks > 65535 || row_tiles > 65535) return LRM_UNSUPPORTED;
+  auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  if (x_dtype == LRM_BF16 && w_dtype == LRM_BF16 && m % 8 == 0 && x_row % 8 == 0 && x_block % 8 == 0 && aligned(x) &&
+      aligned(w)) {
+    const dim3 mma_grid((n + kTile - 1) / kTile, blocks, (tokens + kTile - 1) / kTile);
+    if (out_dtype == LRM_BF16) {
+      LRM_LAUNCH(blockwise_linear_mma_kernel<__nv_bfloat16>, mma_grid, kThreads, 0, stream,
+                 static_cast<const __nv_bfloat16*>(x), x_row, x_block, static_cast<const __nv_bfloat16*>(w), bias,
+                 row_scale, static_cast<__nv_bfloat16*>(out), out_row, out_block, tokens, blocks, n, m);
+      return 0;
+    }
+    if (out_dtype == LRM_F32) {
+      LRM_LAUNCH(blockwise_linear_mma_kernel<float>, mma_grid, kThreads, 0, stream,
+                 static_cast<const __nv_bfloat16*>(x), x_row, x_block, static_cast<const __nv_bfloat16*>(w), bias,
+                 row_scale, static_cast<float*>(out), out_row, out_block, tokens, blocks, n, m);
+      return 0;
+    }
+  }
   const dim3 grid((n + kCols - 1) / kCols, blocks, row_tiles);
 #define LRM_BLOCKWISE(XT, WT, OT)                                                                               \
   do {                                                                                                          \

@@ -117,6 +117,7 @@ __global__ void gated_scan_serial_kernel(ScanInputs<U> in, float* __restrict__ s
   const int slot = slots[b];
   const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
   float s = slot >= 0 ? state[static_cast<size_t>(slot) * in.C + c] : 0.f;
+#pragma unroll 4
   for (int t = t0; t < t1; ++t) {
     float a, x;
     in.step(t, c, rate_c, a, x);
@@ -126,7 +127,7 @@ __global__ void gated_scan_serial_kernel(ScanInputs<U> in, float* __restrict__ s
   if (slot >= 0) state[static_cast<size_t>(slot) * in.C + c] = s;
 }
 
-constexpr int kChunks = 16;  // runs a long portion is cut into (warp-rows of a CTA)
+constexpr int kChunks = 32;  // runs a long portion is cut into (warp-rows of a CTA)
 
 template <typename U, typename O>
 __global__ __launch_bounds__(32 * kChunks) void gated_scan_chunked_kernel(
@@ -143,6 +144,7 @@ __global__ __launch_bounds__(32 * kChunks) void gated_scan_chunked_kernel(
   const int lo = t0 + min(m, run * per), hi = t0 + min(m, (run + 1) * per);
   float s = 0.f, prod = 1.f;
   if (live)
+#pragma unroll 4
     for (int t = lo; t < hi; ++t) {
       float a, x;
       in.step(t, c, rate_c, a, x);
@@ -165,6 +167,7 @@ __global__ __launch_bounds__(32 * kChunks) void gated_scan_chunked_kernel(
   pdl_trigger();
   if (!live) return;
   s = carry[run][threadIdx.x];
+#pragma unroll 4
   for (int t = lo; t < hi; ++t) {
     float a, x;
     in.step(t, c, rate_c, a, x);

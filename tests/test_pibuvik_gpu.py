@@ -567,23 +567,27 @@ def test_window_edges_over_keys_that_hold_their_values(dtype, H, width, dv, wind
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_block_products_with_strides_bias_and_row_scale(dtype):
+@pytest.mark.parametrize("T,B,n,m,lead,gap", [(70, 3, 37, 21, 5, 4), (150, 5, 100, 48, 8, 8), (9, 2, 64, 160, 0, 0)])
+def test_block_products_with_strides_bias_and_row_scale(dtype, T, B, n, m, lead, gap):
+    """Blocks inside wider rows on both sides; the second and third shapes start every block on a
+    16-byte boundary, which in bfloat16 is the tensor-core kernel's case."""
     from llama_rs_metal_b200.kernels import ops
-    gen = torch.Generator().manual_seed(4)
-    T, B, n, m = 70, 3, 37, 21
-    x = torch.randn(T, 5 + B * (m + 4), generator=gen).to(dtype)
+    gen = torch.Generator().manual_seed(4 + m)
+    x = torch.randn(T, lead + B * (m + gap), generator=gen).to(dtype)
     w = torch.randn(B, n, m, generator=gen).to(dtype)
     bias, scale = torch.randn(B, n, generator=gen), torch.rand(T, B, generator=gen)
-    blocks = torch.stack([x[:, 5 + b * (m + 4):5 + b * (m + 4) + m] for b in range(B)], dim=1).to(F64)
+    blocks = torch.stack([x[:, lead + b * (m + gap):lead + b * (m + gap) + m] for b in range(B)], dim=1).to(F64)
     want = (torch.einsum("tbi,boi->tbo", blocks, w.to(F64)) + bias.to(F64)) * scale.to(F64)[:, :, None]
-    out = torch.full((T, 2 + B * (n + 1)), 7.0, dtype=torch.float32, device=DEV)
-    ops.blockwise_linear(x.to(DEV), w.to(DEV), bias=bias.to(DEV), row_scale=scale.to(DEV), x_column=5, x_block=m + 4,
-                         out=out, out_column=2, out_block=n + 1)
-    got = torch.stack([out[:, 2 + b * (n + 1):2 + b * (n + 1) + n] for b in range(B)], dim=1).cpu().to(F64)
     tol = 1e-5 if dtype == torch.float32 else 1e-2
-    assert (got - want).abs().max() <= tol * want.abs().max()
-    assert float(out[:, :2].min()) == 7.0 and float(out[:, 2 + n].min()) == 7.0          # nothing beside the blocks
-    plain = ops.blockwise_linear(x[:, 5:5 + m].contiguous().to(DEV), w[:1].contiguous().to(DEV)).float().cpu()
+    for out_dtype in (torch.float32, dtype):
+        out = torch.full((T, 2 + B * (n + 1)), 7.0, dtype=out_dtype, device=DEV)
+        ops.blockwise_linear(x.to(DEV), w.to(DEV), bias=bias.to(DEV), row_scale=scale.to(DEV), x_column=lead,
+                             x_block=m + gap, out=out, out_column=2, out_block=n + 1)
+        got = torch.stack([out[:, 2 + b * (n + 1):2 + b * (n + 1) + n] for b in range(B)], dim=1).cpu().to(F64)
+        assert (got - want).abs().max() <= tol * want.abs().max()
+        assert float(out[:, :2].min()) == 7.0 and float(out[:, 2 + n].min()) == 7.0          # nothing beside the blocks
+    first = x[:, lead:lead + m].contiguous()
+    plain = ops.blockwise_linear(first.to(DEV), w[:1].contiguous().to(DEV)).float().cpu()
     assert (plain.to(F64) - blocks[:, 0] @ w[0].to(F64).T).abs().max() <= (1e-5 if dtype == torch.float32 else 2e-2) * want.abs().max()
 
 

@@ -153,6 +153,31 @@ def test_prefill_then_decoding_in_an_unequal_batch(engine, folders, plain, name,
     runner.check_device_status()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["P1", "P2"])
+def test_a_prompt_geometry_that_comes_again_is_captured_and_replayed(engine, folders, plain, name, dtype):
+    """Short prompt batches are filled up to whole rows, and a geometry seen before runs as a
+    captured graph: the same shape of batch four times with other tokens, in slots that were used
+    before (state and tails must start from zero each time, also under replay)."""
+    runner, cache, _ = open_runner(engine, folders[name], dtype)
+    V = vocab_of(name)
+    for round_ in range(4):
+        seqs = [helpers.random_tokens(500 + 10 * round_ + i, n, V) for i, n in enumerate([70, 3, 41])]
+        slots = [cache.open_slot() for _ in seqs]
+        out = runner.step([entry(sl, s) for sl, s in zip(slots, seqs)]).cpu().numpy()
+        row = 0
+        for s in seqs:
+            close(out[row:row + len(s)], reference(plain, name, s), dtype, f"{name} round {round_}")
+            row += len(s)
+        nxt = [int(t) for t in helpers.random_tokens(900 + round_, len(seqs), V)]
+        out = runner.step([entry(sl, [t]) for sl, t in zip(slots, nxt)]).cpu().numpy()
+        for i, (s, t) in enumerate(zip(seqs, nxt)):
+            close(out[i:i + 1], reference(plain, name, s + [t])[-1:], dtype, f"{name} round {round_}, next token")
+        for sl in slots:
+            cache.close_slot(sl)
+    runner.check_device_status()
+
+
 @pytest.mark.parametrize("sizes", [[2], [3, 64, 5], [1, 70, 2], [64], [17]])
 @pytest.mark.parametrize("name", ["P1", "P2"])
 def test_portions_of_any_size_give_the_whole_prompt(engine, folders, plain, name, sizes):

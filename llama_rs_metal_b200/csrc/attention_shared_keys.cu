@@ -16,6 +16,10 @@
 // started sequences, and decoding (keys: the paged cache, which already holds the step's rows).
 // A window w lets the query at position p see keys p - w + 1 .. p. Rows of a tile outside the
 // range a CTA's queries can see are zero-filled on the way into shared memory.
+// Decoding offers few CTAs (sequences x groups of 16 heads), so there the key tiles of a sequence
+// may be cut into splits, a CTA each: a split leaves its rows unnormalized with their maximum and
+// mass ([sequence][head][split][DV + 2] float32) and a second kernel merges the splits in order,
+// out = sum acc_i 2^(m_i - M) / sum l_i 2^(m_i - M).
 // DK a multiple of 16, DV a multiple of 16 up to 512; anything else runs the row-wise kernel.
 #include "attention_mma.cuh"
 
@@ -35,6 +39,8 @@ struct SharedKeysArgs {
   const int* slots;
   int table_stride, H, DK, DV, rows_per_query, queries_per_cta, window;
   float scale_log2;
+  float* partials;                // with n_splits > 1 (one query per sequence): blockIdx.x is the split
+  int n_splits;
 };
 
 template <int PAIRS>  // 16-column blocks of the values one warp accumulates (DV <= 64 * PAIRS)
@@ -51,13 +57,33 @@ __global__ __launch_bounds__(kThreads) void attention_shared_keys_kernel(SharedK
   const int b = blockIdx.z;
   const int start = a.cu_seqlens != nullptr ? a.cu_seqlens[b] : b;
   const int n = a.cu_seqlens != nullptr ? a.cu_seqlens[b + 1] - start : 1;
-  const int q0 = blockIdx.x * a.queries_per_cta;
+  const bool split_keys = a.n_splits > 1;
+  const int q0 = split_keys ? 0 : blockIdx.x * a.queries_per_cta;
   if (q0 >= n) return;
   const int len = a.kv_lens != nullptr ? a.kv_lens[b] : n;
   const int before = len - n;
   const int head0 = blockIdx.y * kRowsPerCta;  // more than 16 heads: a CTA takes 16 of one token's
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 
+  const int p_lo = before + q0, p_hi = before + min(q0 + a.queries_per_cta, n) - 1;
+  const int first_key = a.window > 0 ? max(0, p_lo - a.window + 1) : 0;
+  int kt_first = first_key / kTile, kt_last = p_hi / kTile;
+  if (split_keys) {  // this CTA's share of the tiles
+    const int per = (kt_last - kt_first + a.n_splits) / a.n_splits;
+    kt_first += static_cast<int>(blockIdx.x) * per;
+    kt_last = min(kt_last, kt_first + per - 1);
+    if (kt_first > kt_last) {  // more splits than this sequence has tiles: a part that saw no key
+      for (int r = threadIdx.x; r < kRowsPerCta; r += kThreads) {
+        const int head = head0 + r % a.rows_per_query;
+        if (r / a.rows_per_query == 0 && head < a.H) {
+          float* part = a.partials + ((static_cast<size_t>(b) * a.H + head) * a.n_splits + blockIdx.x) * (a.DV + 2);
+          part[a.DV] = -INFINITY;
+          part[a.DV + 1] = 0.f;
+        }
+      }
+      return;
+    }
+  }
   // row r of the CTA: query q0 + r / rows_per_query, head head0 + r % rows_per_query
   for (int idx = threadIdx.x; idx < kRowsPerCta * CHUNKS; idx += kThreads) {
     const int r = idx / CHUNKS, c = idx % CHUNKS;
@@ -73,9 +99,6 @@ __global__ __launch_bounds__(kThreads) void attention_shared_keys_kernel(SharedK
     const int qi = q0 + r / a.rows_per_query, head = head0 + r % a.rows_per_query;
     pos[half] = (qi < n && head < a.H) ? before + qi : -1;  // -1: a row of padding sees no key
   }
-  const int p_lo = before + q0, p_hi = before + min(q0 + a.queries_per_cta, n) - 1;
-  const int first_key = a.window > 0 ? max(0, p_lo - a.window + 1) : 0;
-  const int kt_first = first_key / kTile, kt_last = p_hi / kTile;
   const int* table = a.k_pages != nullptr ? a.page_table + static_cast<size_t>(a.slots[b]) * a.table_stride : nullptr;
 
   auto issue = [&](int kt, int stage) {
@@ -210,8 +233,25 @@ __global__ __launch_bounds__(kThreads) void attention_shared_keys_kernel(SharedK
     const int r = g + 8 * half;
     if (pos[half] < 0) continue;
     const float mass = wsum[r] + wsum[kRowsPerCta + r] + wsum[2 * kRowsPerCta + r] + wsum[3 * kRowsPerCta + r];
-    const float inv = 1.0f / mass;
     const int qi = q0 + r / a.rows_per_query, head = head0 + r % a.rows_per_query;
+    if (split_keys) {
+      float* part = a.partials + ((static_cast<size_t>(b) * a.H + head) * a.n_splits + blockIdx.x) * (a.DV + 2);
+      if (warp == 0 && t == 0) {
+        part[a.DV] = m[half];
+        part[a.DV + 1] = mass;
+      }
+#pragma unroll
+      for (int pi = 0; pi < PAIRS; ++pi) {
+        const int pair = warp + 4 * pi;
+        if (pair >= value_pairs) continue;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+          *reinterpret_cast<float2*>(part + 16 * pair + 8 * j + 2 * t) =
+              make_float2(o[2 * pi + j][2 * half], o[2 * pi + j][2 * half + 1]);
+      }
+      continue;
+    }
+    const float inv = 1.0f / mass;
     __nv_bfloat16* dst = a.out + (static_cast<size_t>(start + qi) * a.H + head) * a.DV;
 #pragma unroll
     for (int pi = 0; pi < PAIRS; ++pi) {
@@ -222,6 +262,29 @@ __global__ __launch_bounds__(kThreads) void attention_shared_keys_kernel(SharedK
         *reinterpret_cast<uint32_t*>(dst + 16 * pair + 8 * j + 2 * t) =
             pack_bf16(o[2 * pi + j][2 * half] * inv, o[2 * pi + j][2 * half + 1] * inv);
     }
+  }
+}
+
+// One block per (sequence, head): the splits' parts merged in split order.
+__global__ void shared_keys_merge_kernel(const float* __restrict__ partials, __nv_bfloat16* __restrict__ out,
+                                         int n_parts, int DV) {
+  pdl_trigger();
+  pdl_wait();
+  const float* src = partials + static_cast<size_t>(blockIdx.x) * n_parts * (DV + 2);
+  float M = -INFINITY;
+  for (int i = 0; i < n_parts; ++i) M = fmaxf(M, src[i * (DV + 2) + DV]);
+  float mass = 0.f;
+  for (int i = 0; i < n_parts; ++i) {
+    const float mi = src[i * (DV + 2) + DV];
+    if (mi != -INFINITY) mass = fmaf(src[i * (DV + 2) + DV + 1], exp2f(mi - M), mass);
+  }
+  for (int d = threadIdx.x; d < DV; d += blockDim.x) {
+    float acc = 0.f;
+    for (int i = 0; i < n_parts; ++i) {
+      const float mi = src[i * (DV + 2) + DV];
+      if (mi != -INFINITY) acc = fmaf(src[i * (DV + 2) + d], exp2f(mi - M), acc);
+    }
+    out[static_cast<size_t>(blockIdx.x) * DV + d] = __float2bfloat16_rn(acc / mass);
   }
 }
 
@@ -237,6 +300,9 @@ int launch_shared_keys(const SharedKeysArgs& a, dim3 grid, cudaStream_t stream) 
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
   LRM_LAUNCH(kernel, grid, kThreads, smem, stream, a);
+  if (a.n_splits > 1)
+    LRM_LAUNCH(shared_keys_merge_kernel, grid.z * a.H, a.DV >= 256 ? 128 : 64, 0, stream,
+               static_cast<const float*>(a.partials), a.out, a.n_splits, a.DV);
   return 0;
 }
 
@@ -252,17 +318,22 @@ LRM_API int lrm_attention_shared_keys_supports(int heads, int dk, int dv, int pa
 // q [queries, heads, dk], out [queries, heads * dv], bfloat16. A prompt: k_packed [queries, dk], cu_seqlens
 // [seqs + 1], kv_lens null. Over the cache: k_pages with page_table / slots, kv_lens [seqs] the
 // lengths after the step; cu_seqlens [seqs + 1] for portions of several queries (at most
-// `max_queries` per sequence), or null for one query per sequence.
+// `max_queries` per sequence), or null for one query per sequence; only then may the keys be cut into
+// `n_splits` > 1 splits, with `partials` holding seqs * heads * n_splits * (dv + 2) floats.
 LRM_API int lrm_attention_shared_keys(const void* q, const void* k_packed, const void* k_pages, void* out,
                                       const int* cu_seqlens, const int* kv_lens, const int* page_table,
                                       int table_stride, const int* slots, int seqs, int max_queries, int heads,
-                                      int dk, int dv, float scale, int window, cudaStream_t stream) {
+                                      int dk, int dv, float scale, int window, float* partials, int n_splits,
+                                      cudaStream_t stream) {
   if (seqs <= 0 || max_queries <= 0) return 0;
   if (!lrm_attention_shared_keys_supports(heads, dk, dv, kTile)) return LRM_UNSUPPORTED;
   if ((k_packed == nullptr) == (k_pages == nullptr)) return LRM_BAD_ARGUMENT;
   if (k_pages != nullptr && (kv_lens == nullptr || page_table == nullptr || slots == nullptr)) return LRM_BAD_ARGUMENT;
   if (k_packed != nullptr && (cu_seqlens == nullptr || kv_lens != nullptr)) return LRM_BAD_ARGUMENT;
+  if (n_splits > 1 && (cu_seqlens != nullptr || partials == nullptr || n_splits > 65535)) return LRM_BAD_ARGUMENT;
   SharedKeysArgs a;
+  a.partials = partials;
+  a.n_splits = n_splits > 1 ? n_splits : 1;
   a.q = static_cast<const __nv_bfloat16*>(q);
   a.k_packed = static_cast<const __nv_bfloat16*>(k_packed);
   a.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
@@ -290,7 +361,7 @@ LRM_API int lrm_attention_shared_keys(const void* q, const void* k_packed, const
   }
   const int query_tiles = (max_queries + a.queries_per_cta - 1) / a.queries_per_cta;
   if (seqs > 65535 || head_groups > 65535) return LRM_UNSUPPORTED;
-  const dim3 grid(query_tiles, head_groups, seqs);
+  const dim3 grid(a.n_splits > 1 ? a.n_splits : query_tiles, head_groups, seqs);
   const int pairs = (dv / 16 + 3) / 4;
   if (pairs <= 1) return launch_shared_keys<1>(a, grid, stream);
   if (pairs <= 2) return launch_shared_keys<2>(a, grid, stream);

@@ -32,6 +32,7 @@ force_rowwise = False  # tests switch the tiled kernels off to compare both path
 force_warp_level = False  # tests keep prompts off the tcgen05 kernel to cover the warp-level one
 force_unfused_decode = False  # tests keep decode steps on the separate rotation / attention / merge kernels
 force_cluster_size = None  # tests fix the CTAs per cluster of the fused decode kernel
+force_shared_key_splits = None  # tests fix the splits of the shared-key kernel's decode step
 prefill_kernel = None  # tests pin the tcgen05 prompt kernel: "pingpong" or "single" (None: the rule in prefill())
 
 
@@ -98,7 +99,7 @@ def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: flo
         if shared and dv != d and k.data_ptr() % 16 == 0 and _shared_keys(q, k.shape[1], dv, slopes, out_scale, extras):
             _done(lib.lrm_attention_shared_keys(_ptr(q), _ptr(k), None, _ptr(out), _ptr(cu_seqlens), None, None, 0,
                                                 None, cu_seqlens.numel() - 1, max_seq_len, Hq, d, dv,
-                                                ctypes.c_float(scale), window, _stream()),
+                                                ctypes.c_float(scale), window, None, 1, _stream()),
                   "attention_shared_keys")
             return
         if dv == d and _tiled(q, 64) and shared:
@@ -182,10 +183,16 @@ def decode(q, kv, out, slots, kv_lens, max_kv_len: int, scale: float, window: in
     lib = library.load()
     if (getattr(kv, "values_in_keys", False) and dv != d and kv.page_size == 64
             and _shared_keys(q, kv.kv_heads, dv, slopes, out_scale, extras)):
+        # few CTAs (sequences x groups of 16 heads): the key tiles are cut until about two CTAs per SM run
+        keys = min(max_kv_len, window + 63) if window > 0 else max_kv_len
+        splits = max(1, min(-(-keys // 64), 2 * SM_COUNT // (B * -(-Hq // 16))))
+        if force_shared_key_splits is not None:
+            splits = force_shared_key_splits
+        partials = torch.empty((B, Hq, splits, dv + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
         _done(lib.lrm_attention_shared_keys(_ptr(q), None, _ptr(kv.k), _ptr(out), None, _ptr(kv_lens),
                                             _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots), B, 1, Hq, d,
-                                            dv, ctypes.c_float(scale), window, _stream()),
-              "attention_shared_keys")
+                                            dv, ctypes.c_float(scale), window, _ptr(partials), splits, _stream()),
+              "attention_shared_keys", launches=2 if splits > 1 else 1)
         return
     if dv == d and _tiled(q, kv.page_size):
         splits = decode_splits(B, kv.kv_heads, Hq // kv.kv_heads, max_kv_len, window)
@@ -219,7 +226,7 @@ def extend(q, kv, out, cu_seqlens, seq_of_token, positions, slots, kv_lens, max_
         _done(lib.lrm_attention_shared_keys(_ptr(q), None, _ptr(kv.k), _ptr(out), _ptr(cu_seqlens), _ptr(kv_lens),
                                             _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
                                             cu_seqlens.numel() - 1, max_seq_len, Hq, d, dv, ctypes.c_float(scale),
-                                            window, _stream()),
+                                            window, None, 1, _stream()),
               "attention_shared_keys")
         return
     if dv == d and _tiled(q, kv.page_size):

@@ -580,10 +580,17 @@ def test_window_edges_over_keys_that_hold_their_values(dtype, H, width, dv, wind
                                 value_dim=dv).float().cpu()
     assert (got.view(T, H, dv).to(F64) - want).abs().max() <= tol * want.abs().max(), "prompt"
     paged = PagedKeys(rows, 1, dv, window, dtype, seed=window)
-    for pos in probes:
-        got = ops.attention_decode(q[pos:pos + 1].to(DEV), paged.view, _ints([1]), _ints([pos + 1]), pos + 1, scale,
-                                   window).float().cpu()
-        assert (got.view(H, dv).to(F64) - want[pos]).abs().max() <= tol * want.abs().max(), f"decoding at {pos}"
+    from llama_rs_metal_b200.kernels import attention_dispatch
+    for splits in (None, 1, 3, 7):      # the keys of a decode step whole, and cut into more splits than tiles
+        attention_dispatch.force_shared_key_splits = splits
+        try:
+            for pos in probes:
+                got = ops.attention_decode(q[pos:pos + 1].to(DEV), paged.view, _ints([1]), _ints([pos + 1]), pos + 1,
+                                           scale, window).float().cpu()
+                assert (got.view(H, dv).to(F64) - want[pos]).abs().max() <= tol * want.abs().max(), \
+                    f"decoding at {pos} in {splits} splits"
+        finally:
+            attention_dispatch.force_shared_key_splits = None
     lo = 60
     cu, seq = step_arrays([T - lo])
     got = ops.attention_extend(q[lo:].to(DEV), paged.view, cu, seq, _ints(list(range(lo, T))), _ints([1]), _ints([T]),

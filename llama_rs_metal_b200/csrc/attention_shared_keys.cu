@@ -4,13 +4,14 @@
 // folded into the queries and unfolded from the outputs. Warp-level tensor path (mma.sync
 // m16n8k16, ldmatrix, cp.async), float32 softmax in the log2 domain.
 //
-// One CTA = 16 query rows (the heads of one token; several tokens when a token has 8 heads or
-// fewer; 16 heads of a token at a time when it has more) against 64-key tiles, double buffered.
-// Because all rows read the same keys, the four warps share a tile's work by columns instead of
-// by rows: each warp scores its 16 keys of the tile for all 16 rows; the rows' maxima meet in
-// shared memory, the probabilities are written there as bfloat16, and each warp then multiplies
-// all of them with its own 16-column blocks of the values (blocks w, w + 4, ...). A warp so holds
-// DV / 4 accumulator columns, which is what lets DV be 256 or 512 without spilling.
+// One CTA = 32 query rows in two groups of 16 (the heads of two tokens; more tokens when a token
+// has 8 heads or fewer; 32 heads of a token at a time when it has more) against 64-key tiles,
+// double buffered, which both groups read. Because all rows read the same keys, the four warps of
+// a group share a tile's work by columns instead of by rows: each warp scores its 16 keys of the
+// tile for the group's 16 rows; the rows' maxima meet in shared memory, the probabilities are
+// written there as bfloat16, and each warp then multiplies all of them with its own 16-column
+// blocks of the values (blocks w, w + 4, ...). A warp so holds DV / 4 accumulator columns, which
+// is what lets DV be 256 or 512 without spilling.
 //
 // The same kernel serves a prompt (keys: the step's own packed rows), a portion appended to
 // started sequences, and decoding (keys: the paged cache, which already holds the step's rows).
@@ -25,7 +26,8 @@
 
 namespace {
 
-constexpr int kRowsPerCta = 16;
+constexpr int kRowsPerCta = 32;   // two groups of 16 rows, four warps each
+constexpr int kSkThreads = 256;
 constexpr int kProbStride = kTile + 8;
 
 struct SharedKeysArgs {
@@ -44,14 +46,14 @@ struct SharedKeysArgs {
 };
 
 template <int PAIRS>  // 16-column blocks of the values one warp accumulates (DV <= 64 * PAIRS)
-__global__ __launch_bounds__(kThreads) void attention_shared_keys_kernel(SharedKeysArgs a) {
+__global__ __launch_bounds__(kSkThreads) void attention_shared_keys_kernel(SharedKeysArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int STRIDE = a.DK + 8, CHUNKS = a.DK / 8;
-  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [16][STRIDE]
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [32][STRIDE]
   __nv_bfloat16* Ks = Qs + kRowsPerCta * STRIDE;                    // [2][64][STRIDE]
-  __nv_bfloat16* Ps = Ks + 2 * kTile * STRIDE;                      // [16][kProbStride]
-  float* wmax = reinterpret_cast<float*>(Ps + kRowsPerCta * kProbStride);  // [4][16]
-  float* wsum = wmax + 4 * kRowsPerCta;                             // [4][16]
+  __nv_bfloat16* Ps = Ks + 2 * kTile * STRIDE;                      // [32][kProbStride]
+  float* wmax = reinterpret_cast<float*>(Ps + kRowsPerCta * kProbStride);  // [group][warp of the group][16]
+  float* wsum = wmax + 8 * 16;
 
   pdl_wait();
   const int b = blockIdx.z;
@@ -62,8 +64,11 @@ __global__ __launch_bounds__(kThreads) void attention_shared_keys_kernel(SharedK
   if (q0 >= n) return;
   const int len = a.kv_lens != nullptr ? a.kv_lens[b] : n;
   const int before = len - n;
-  const int head0 = blockIdx.y * kRowsPerCta;  // more than 16 heads: a CTA takes 16 of one token's
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int head0 = blockIdx.y * kRowsPerCta;  // more than 32 heads: a CTA takes 32 of one token's
+  const int group = threadIdx.x >> 7, warp = (threadIdx.x >> 5) & 3;  // row group, and the warp's place in it
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  float* gmax = wmax + group * 64;
+  float* gsum = wsum + group * 64;
 
   const int p_lo = before + q0, p_hi = before + min(q0 + a.queries_per_cta, n) - 1;
   const int first_key = a.window > 0 ? max(0, p_lo - a.window + 1) : 0;
@@ -73,7 +78,7 @@ __global__ __launch_bounds__(kThreads) void attention_shared_keys_kernel(SharedK
     kt_first += static_cast<int>(blockIdx.x) * per;
     kt_last = min(kt_last, kt_first + per - 1);
     if (kt_first > kt_last) {  // more splits than this sequence has tiles: a part that saw no key
-      for (int r = threadIdx.x; r < kRowsPerCta; r += kThreads) {
+      for (int r = threadIdx.x; r < kRowsPerCta; r += kSkThreads) {
         const int head = head0 + r % a.rows_per_query;
         if (r / a.rows_per_query == 0 && head < a.H) {
           float* part = a.partials + ((static_cast<size_t>(b) * a.H + head) * a.n_splits + blockIdx.x) * (a.DV + 2);
@@ -85,7 +90,7 @@ __global__ __launch_bounds__(kThreads) void attention_shared_keys_kernel(SharedK
     }
   }
   // row r of the CTA: query q0 + r / rows_per_query, head head0 + r % rows_per_query
-  for (int idx = threadIdx.x; idx < kRowsPerCta * CHUNKS; idx += kThreads) {
+  for (int idx = threadIdx.x; idx < kRowsPerCta * CHUNKS; idx += kSkThreads) {
     const int r = idx / CHUNKS, c = idx % CHUNKS;
     const int qi = q0 + r / a.rows_per_query, head = head0 + r % a.rows_per_query;
     const bool ok = qi < n && head < a.H;
@@ -95,7 +100,7 @@ __global__ __launch_bounds__(kThreads) void attention_shared_keys_kernel(SharedK
   int pos[2];
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
-    const int r = g + 8 * half;
+    const int r = 16 * group + g + 8 * half;
     const int qi = q0 + r / a.rows_per_query, head = head0 + r % a.rows_per_query;
     pos[half] = (qi < n && head < a.H) ? before + qi : -1;  // -1: a row of padding sees no key
   }
@@ -112,7 +117,7 @@ __global__ __launch_bounds__(kThreads) void attention_shared_keys_kernel(SharedK
     } else {
       base = a.k_packed + static_cast<size_t>(start + kt * kTile) * a.DK;
     }
-    for (int idx = threadIdx.x; idx < kTile * CHUNKS; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < kTile * CHUNKS; idx += kSkThreads) {
       const int r = idx / CHUNKS, c = idx % CHUNKS;
       const int key = kt * kTile + r;
       const bool ok = held && key >= first_key && key <= p_hi;
@@ -143,7 +148,7 @@ __global__ __launch_bounds__(kThreads) void attention_shared_keys_kernel(SharedK
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
-    const __nv_bfloat16* q_at = Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + 8 * (lane >> 4);
+    const __nv_bfloat16* q_at = Qs + (16 * group + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + 8 * (lane >> 4);
     const __nv_bfloat16* k_at = Kt + (16 * warp + (lane & 7) + 8 * (lane >> 4)) * STRIDE + 8 * ((lane >> 3) & 1);
 #pragma unroll 2
     for (int ks = 0; ks < a.DK / 16; ++ks) {
@@ -169,15 +174,14 @@ __global__ __launch_bounds__(kThreads) void attention_shared_keys_kernel(SharedK
     for (int half = 0; half < 2; ++half) {
       mx[half] = fmaxf(mx[half], __shfl_xor_sync(0xffffffffu, mx[half], 1));
       mx[half] = fmaxf(mx[half], __shfl_xor_sync(0xffffffffu, mx[half], 2));
-      if (t == 0) wmax[warp * kRowsPerCta + g + 8 * half] = mx[half];
+      if (t == 0) gmax[warp * 16 + g + 8 * half] = mx[half];
     }
     __syncthreads();
     float alpha[2];
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int r = g + 8 * half;
-      const float tile_max = fmaxf(fmaxf(wmax[r], wmax[kRowsPerCta + r]),
-                                   fmaxf(wmax[2 * kRowsPerCta + r], wmax[3 * kRowsPerCta + r]));
+      const float tile_max = fmaxf(fmaxf(gmax[r], gmax[16 + r]), fmaxf(gmax[32 + r], gmax[48 + r]));
       const float m_new = fmaxf(m[half], tile_max);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row with no visible key yet
       alpha[half] = exp2_fast(m[half] - m_use);
@@ -186,7 +190,7 @@ __global__ __launch_bounds__(kThreads) void attention_shared_keys_kernel(SharedK
       for (int nt = 0; nt < 2; ++nt) {
         const float p0 = exp2_fast(s[nt][2 * half] - m_use), p1 = exp2_fast(s[nt][2 * half + 1] - m_use);
         sum += p0 + p1;
-        *reinterpret_cast<uint32_t*>(Ps + r * kProbStride + 16 * warp + 8 * nt + 2 * t) = pack_bf16(p0, p1);
+        *reinterpret_cast<uint32_t*>(Ps + (16 * group + r) * kProbStride + 16 * warp + 8 * nt + 2 * t) = pack_bf16(p0, p1);
       }
       l[half] = l[half] * alpha[half] + sum;
       m[half] = m_new;
@@ -200,7 +204,7 @@ __global__ __launch_bounds__(kThreads) void attention_shared_keys_kernel(SharedK
     }
     __syncthreads();
     // this warp's value blocks: all 64 probabilities of every row times 16 columns at a time
-    const __nv_bfloat16* p_at = Ps + ((lane & 7) + 8 * ((lane >> 3) & 1)) * kProbStride + 8 * (lane >> 4);
+    const __nv_bfloat16* p_at = Ps + (16 * group + (lane & 7) + 8 * ((lane >> 3) & 1)) * kProbStride + 8 * (lane >> 4);
     const __nv_bfloat16* v_at = Kt + ((lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + 8 * (lane >> 4);
 #pragma unroll
     for (int kk = 0; kk < kTile / 16; ++kk) {
@@ -225,14 +229,14 @@ __global__ __launch_bounds__(kThreads) void attention_shared_keys_kernel(SharedK
     float total = l[half];
     total += __shfl_xor_sync(0xffffffffu, total, 1);
     total += __shfl_xor_sync(0xffffffffu, total, 2);
-    if (t == 0) wsum[warp * kRowsPerCta + g + 8 * half] = total;
+    if (t == 0) gsum[warp * 16 + g + 8 * half] = total;
   }
   __syncthreads();
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
-    const int r = g + 8 * half;
+    const int r16 = g + 8 * half, r = 16 * group + r16;
     if (pos[half] < 0) continue;
-    const float mass = wsum[r] + wsum[kRowsPerCta + r] + wsum[2 * kRowsPerCta + r] + wsum[3 * kRowsPerCta + r];
+    const float mass = gsum[r16] + gsum[16 + r16] + gsum[32 + r16] + gsum[48 + r16];
     const int qi = q0 + r / a.rows_per_query, head = head0 + r % a.rows_per_query;
     if (split_keys) {
       float* part = a.partials + ((static_cast<size_t>(b) * a.H + head) * a.n_splits + blockIdx.x) * (a.DV + 2);
@@ -290,7 +294,7 @@ __global__ void shared_keys_merge_kernel(const float* __restrict__ partials, __n
 
 size_t shared_keys_smem(int DK) {
   return static_cast<size_t>(kRowsPerCta + 2 * kTile) * (DK + 8) * 2 + kRowsPerCta * kProbStride * 2 +
-         2 * 4 * kRowsPerCta * sizeof(float);
+         2 * 8 * 16 * sizeof(float);
 }
 
 template <int PAIRS>
@@ -299,7 +303,7 @@ int launch_shared_keys(const SharedKeysArgs& a, dim3 grid, cudaStream_t stream) 
   auto kernel = attention_shared_keys_kernel<PAIRS>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
-  LRM_LAUNCH(kernel, grid, kThreads, smem, stream, a);
+  LRM_LAUNCH(kernel, grid, kSkThreads, smem, stream, a);
   if (a.n_splits > 1)
     LRM_LAUNCH(shared_keys_merge_kernel, grid.z * a.H, a.DV >= 256 ? 128 : 64, 0, stream,
                static_cast<const float*>(a.partials), a.out, a.n_splits, a.DV);

@@ -344,9 +344,76 @@ __global__ void rms_norm_add_kernel(float* __restrict__ stream, const float* __r
   }
 }
 
+// The same with 16-byte accesses (hidden % 4 == 0, 16-byte aligned rows): a thread keeps PER4 groups
+// of four consecutive elements.
+template <typename W, typename O, int PER4>
+__global__ void rms_norm_add_vec_kernel(float* __restrict__ stream, const float* __restrict__ y,
+                                        const W* __restrict__ w, float mult, float eps, const W* __restrict__ w2,
+                                        O* __restrict__ out2, float eps2, int hidden) {
+  __shared__ float scratch[32];
+  const int groups = hidden >> 2;
+  float4 wv[PER4], w2v[PER4];
+#pragma unroll
+  for (int e = 0; e < PER4; ++e) {  // weights do not depend on the kernel before this one
+    const int c = threadIdx.x + e * blockDim.x;
+    wv[e] = c < groups ? load4(w + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    w2v[e] = (w2 != nullptr && c < groups) ? load4(w2 + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = static_cast<size_t>(blockIdx.x) * hidden;
+  float4 yv[PER4], sv[PER4];
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < PER4; ++e) {
+    const int c = threadIdx.x + e * blockDim.x;
+    yv[e] = c < groups ? load4(y + row + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    sv[e] = c < groups ? load4(stream + row + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss = fmaf(yv[e].x, yv[e].x, fmaf(yv[e].y, yv[e].y, fmaf(yv[e].z, yv[e].z, fmaf(yv[e].w, yv[e].w, ss))));
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / static_cast<float>(hidden) + eps);
+  float ss2 = 0.f;
+#pragma unroll
+  for (int e = 0; e < PER4; ++e) {
+    const int c = threadIdx.x + e * blockDim.x;
+    if (c < groups) {
+      float4 v;
+      v.x = sv[e].x + mult * ((yv[e].x * inv) * wv[e].x);
+      v.y = sv[e].y + mult * ((yv[e].y * inv) * wv[e].y);
+      v.z = sv[e].z + mult * ((yv[e].z * inv) * wv[e].z);
+      v.w = sv[e].w + mult * ((yv[e].w * inv) * wv[e].w);
+      store4(stream + row + 4 * c, v);
+      sv[e] = v;
+      ss2 = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss2))));
+    }
+  }
+  if (w2 == nullptr) return;
+  const float inv2 = 1.0f / sqrtf(block_sum(ss2, scratch) / static_cast<float>(hidden) + eps2);
+#pragma unroll
+  for (int e = 0; e < PER4; ++e) {
+    const int c = threadIdx.x + e * blockDim.x;
+    if (c < groups)
+      store4(out2 + row + 4 * c, make_float4((sv[e].x * inv2) * w2v[e].x, (sv[e].y * inv2) * w2v[e].y,
+                                             (sv[e].z * inv2) * w2v[e].z, (sv[e].w * inv2) * w2v[e].w));
+  }
+}
+
 template <typename W, typename O>
 static int launch_norm_add(float* stream, const float* y, const void* w, float mult, float eps, const void* w2,
                            void* out2, float eps2, int n_rows, int hidden, cudaStream_t stream_handle) {
+  auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  if (hidden % 4 == 0 && aligned(stream) && aligned(y) && aligned(w) && aligned(w2) && aligned(out2)) {
+    const int groups = hidden / 4;
+    const int vthreads = groups > 2048 ? 1024 : (groups >= 512 ? 256 : (groups >= 64 ? 128 : 32));
+    const int per4 = (groups + vthreads - 1) / vthreads;
+#define LRM_NORM_ADD_VEC(P4)                                                                                  \
+  return static_cast<int>(lrm_launch(rms_norm_add_vec_kernel<W, O, P4>, n_rows, vthreads, 0, stream_handle,  \
+                                     stream, y, static_cast<const W*>(w), mult, eps,                          \
+                                     static_cast<const W*>(w2), static_cast<O*>(out2), eps2, hidden))
+    if (per4 <= 2) LRM_NORM_ADD_VEC(2);
+    if (per4 <= 8) LRM_NORM_ADD_VEC(8);
+#undef LRM_NORM_ADD_VEC
+  }
   const int threads = hidden > 2048 ? 1024 : (hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 32));
   const int per = (hidden + threads - 1) / threads;
 #define LRM_NORM_ADD(PER)                                                                                  \

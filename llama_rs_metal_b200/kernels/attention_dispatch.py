@@ -183,9 +183,9 @@ def decode(q, kv, out, slots, kv_lens, max_kv_len: int, scale: float, window: in
     lib = library.load()
     if (getattr(kv, "values_in_keys", False) and dv != d and kv.page_size == 64
             and _shared_keys(q, kv.kv_heads, dv, slopes, out_scale, extras)):
-        # few CTAs (sequences x groups of 16 heads): the key tiles are cut until about two CTAs per SM run
+        # few CTAs (sequences x groups of 32 heads): the key tiles are cut until about two CTAs per SM run
         keys = min(max_kv_len, window + 63) if window > 0 else max_kv_len
-        splits = max(1, min(-(-keys // 64), 2 * SM_COUNT // (B * -(-Hq // 16))))
+        splits = max(1, min(-(-keys // 64), 2 * SM_COUNT // (B * -(-Hq // 32))))
         if force_shared_key_splits is not None:
             splits = force_shared_key_splits
         partials = torch.empty((B, Hq, splits, dv + 2), dtype=torch.float32, device=q.device) if splits > 1 else None

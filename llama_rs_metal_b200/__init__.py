@@ -1,5 +1,6 @@
 """A small B200-native inference library for decoders put together from registered parts: the
-Llama 3 dense decoder and the Kikalix decoder (state mixers, windowed attention, experts).
+Llama 3 dense decoder, the Kikalix decoder (state mixers, windowed attention, experts) and the
+Pibuvik decoder (a gated recurrence, attention with sinks, latent attention, sandwich norms).
 
 Public surface (after crates/llama-rs/src/lib.rs): Engine, Model, Session,
 GenerationOptions, Sampling, GenerationResult, and the typed errors.
